@@ -26,8 +26,9 @@ template <typename S, int TOK>
 __global__ void __launch_bounds__(kRouteWarps * 32)
     moe_route_kernel(const S* __restrict__ x, long long ld_x, const float* __restrict__ w,
                      const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights, int T, int D,
-                     int E, int top) {
-  extern __shared__ __align__(16) float route_smem[];  // rows [TOK][Dpad] | logits [TOK][E]
+                     int E, int top, int scored, const float* __restrict__ correction, int groups, int keep,
+                     float scale, const float* __restrict__ gate_w, float* __restrict__ gate_out) {
+  extern __shared__ __align__(16) float route_smem[];  // rows [TOK][Dpad] | logits [TOK][E] (scored: | scores, group scores [TOK][2E])
   const int Dpad = (D + 3) & ~3;
   float* rows = route_smem;
   float* logits = route_smem + TOK * Dpad;
@@ -40,12 +41,15 @@ __global__ void __launch_bounds__(kRouteWarps * 32)
     for (int i = threadIdx.x; i < Dpad; i += blockDim.x)
       rows[r * Dpad + i] = (r < nt && i < D) ? ldf(x + static_cast<long long>(t0 + r) * ld_x + i) : 0.f;
   __syncthreads();
-  const bool vec = (D & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
-  for (int e = warp; e < E; e += kRouteWarps) {
+  const bool vec = (D & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(gate_w) & 15) == 0;
+  // (gate_w: one more row, whose product goes through a sigmoid into gate_out[t]: a gate per token that reads the
+  // router's input, such as a shared expert's)
+  const int n_rows = E + (gate_w ? 1 : 0);
+  for (int e = warp; e < n_rows; e += kRouteWarps) {
     float acc[TOK];
 #pragma unroll
     for (int r = 0; r < TOK; ++r) acc[r] = 0.f;
-    const float* wr = w + static_cast<size_t>(e) * D;
+    const float* wr = e < E ? w + static_cast<size_t>(e) * D : gate_w;
     if (vec) {
       for (int i = lane * 4; i < D; i += 128) {
         const float4 wv = *reinterpret_cast<const float4*>(wr + i);
@@ -65,10 +69,89 @@ __global__ void __launch_bounds__(kRouteWarps * 32)
 #pragma unroll
     for (int r = 0; r < TOK; ++r) {
       const float sum = warp_sum(acc[r]);
-      if (lane == 0) logits[r * E + e] = sum + (bias ? bias[e] : 0.f);
+      if (lane == 0) {
+        if (e < E) logits[r * E + e] = sum + (bias ? bias[e] : 0.f);
+        else if (r < nt) gate_out[t0 + r] = 1.f / (1.f + expf(-sum));
+      }
     }
   }
   __syncthreads();
+  if (scored) {
+    // Scores s = sigmoid(z).  The choice runs on s + correction, among the experts of the `keep` groups (of `groups`
+    // equal groups of neighbours) whose two largest choice scores sum highest; every other expert's choice score is
+    // -inf.  The weights are the chosen s over their sum (+ 1e-20), times scale.  The lower index wins a tie.
+    float* extra = logits + TOK * E;
+    for (int r = warp; r < nt; r += kRouteWarps) {
+      float* z = logits + r * E;         // becomes the choice scores
+      float* sc = extra + r * 2 * E;     // s
+      float* gs = sc + E;                // group scores
+      for (int e = lane; e < E; e += 32) {
+        const float sv = 1.f / (1.f + expf(-z[e]));
+        sc[e] = sv;
+        z[e] = sv + (correction ? correction[e] : 0.f);
+      }
+      __syncwarp();
+      if (groups > 1) {
+        const int per = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+          float a = -INFINITY, b = -INFINITY;  // the largest and the second largest
+          for (int e = g * per; e < (g + 1) * per; ++e) {
+            const float v = z[e];
+            if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+          }
+          gs[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // the `keep` best groups are marked by +inf in gs; then the others' experts drop out
+        for (int j = 0; j < keep; ++j) {
+          float best = -INFINITY;
+          int arg = 0x7fffffff;
+          for (int g = lane; g < groups; g += 32) {
+            const float v = gs[g];
+            if (v != INFINITY && (v > best || (v == best && g < arg) || arg == 0x7fffffff)) { best = v; arg = g; }
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
+          }
+          if (lane == 0 && arg < groups) gs[arg] = INFINITY;
+          __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+          if (gs[e / per] != INFINITY) z[e] = -INFINITY;
+        __syncwarp();
+      }
+      float denom = 0.f;
+      for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+          const float v = z[e];
+          if (v > best || (v == best && e < arg)) { best = v; arg = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+          if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg >= E) arg = j;  // nothing left to choose from: keep the indices valid
+        const float p = sc[arg];
+        denom += p;
+        if (lane == 0) {
+          ids[static_cast<size_t>(t0 + r) * top + j] = arg;
+          weights[static_cast<size_t>(t0 + r) * top + j] = p;
+          z[arg] = -INFINITY;
+        }
+        __syncwarp();
+      }
+      const float inv = scale / (denom + 1e-20f);
+      for (int j = lane; j < top; j += 32) weights[static_cast<size_t>(t0 + r) * top + j] *= inv;
+    }
+    return;
+  }
   for (int r = warp; r < nt; r += kRouteWarps) {
     float* z = logits + r * E;
     float first = 0.f, denom = 0.f;
@@ -205,6 +288,12 @@ __device__ __forceinline__ float clamped_glu(float g, float u, float limit, floa
   return g / (1.f + expf(-alpha * g)) * (u + shift);
 }
 
+// The ungated experts' activation: max(z, 0)^2.
+__device__ __forceinline__ float relu_squared(float z) {
+  z = fmaxf(z, 0.f);
+  return z * z;
+}
+
 // Finds the expert and the rows of row tile `tile`; false when there is no such tile.
 __device__ __forceinline__ bool moe_tile(int tile, const int* __restrict__ offsets, const int* __restrict__ tile_start,
                                          int E, int tile_rows, int& e, int& row0, int& row1) {
@@ -231,7 +320,7 @@ __global__ void __launch_bounds__(256)
     moe_gemm_generic_kernel(const S* __restrict__ a, long long ld_a, const S* __restrict__ w,
                             const int* __restrict__ perm, const int* __restrict__ offsets,
                             const int* __restrict__ tile_start, int E, int top, int K, int N, float limit, float alpha,
-                            float shift, void* __restrict__ out) {
+                            float shift, int ungated, void* __restrict__ out) {
   __shared__ float As[kGenRows][kGenK + 1];
   __shared__ float Bs[UP ? 2 : 1][kGenCols][kGenK + 1];
   __shared__ int src_row[kGenRows];
@@ -243,7 +332,7 @@ __global__ void __launch_bounds__(256)
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   if (threadIdx.x < kGenRows) {
     const int i = row0 + threadIdx.x;
-    src_row[threadIdx.x] = i < row1 ? (UP ? perm[i] / top : i) : -1;
+    src_row[threadIdx.x] = i < row1 ? ((UP || ungated) ? perm[i] / top : i) : -1;
   }
   __syncthreads();
   const S* we = w + static_cast<size_t>(e) * (UP ? 2 : 1) * N * K;
@@ -287,7 +376,9 @@ __global__ void __launch_bounds__(256)
       stf(static_cast<S*>(out) + static_cast<size_t>(i) * N + n0 + tx,
           clamped_glu(acc[0][r], acc[UP ? 1 : 0][r], limit, alpha, shift));
     } else {
-      stf(static_cast<S*>(out) + static_cast<size_t>(perm[i]) * N + n0 + tx, acc[0][r]);
+      // (ungated: the activation's rows stay in the order of the sorted pairs, like the gated form's)
+      stf(static_cast<S*>(out) + static_cast<size_t>(ungated ? i : perm[i]) * N + n0 + tx,
+          ungated ? relu_squared(acc[0][r]) : acc[0][r]);
     }
   }
 }
@@ -302,7 +393,7 @@ __global__ void __launch_bounds__(128)
     moe_gemm_mma_kernel(const bf16* __restrict__ a, long long ld_a, const bf16* __restrict__ w,
                         const int* __restrict__ perm, const int* __restrict__ offsets,
                         const int* __restrict__ tile_start, int E, int top, int K, int N, float limit, float alpha,
-                        float shift, void* __restrict__ out) {
+                        float shift, int ungated, void* __restrict__ out) {
   constexpr int BROWS = UP ? 2 * kMmaCols : kMmaCols;
   constexpr int LD = kMmaK + kMmaPad;  // 40 elements = 80 bytes: ldmatrix rows fall into different banks
   __shared__ __align__(16) bf16 As[2][kMmaRows][LD];
@@ -318,7 +409,7 @@ __global__ void __launch_bounds__(128)
   if (threadIdx.x < kMmaRows) {
     const int i = row0 + threadIdx.x;
     const int p = i < row1 ? perm[i] : -1;
-    src_row[threadIdx.x] = i < row1 ? (UP ? p / top : i) : -1;
+    src_row[threadIdx.x] = i < row1 ? ((UP || ungated) ? p / top : i) : -1;
     dst_row[threadIdx.x] = p;
   }
   __syncthreads();
@@ -392,7 +483,9 @@ __global__ void __launch_bounds__(128)
           const float g = acc[j][half * 2 + q], u = acc[UP ? j + kMmaCols / 8 : j][half * 2 + q];
           static_cast<bf16*>(out)[static_cast<size_t>(i) * N + col] = __float2bfloat16_rn(clamped_glu(g, u, limit, alpha, shift));
         } else {
-          static_cast<bf16*>(out)[static_cast<size_t>(dst_row[r]) * N + col] = __float2bfloat16_rn(acc[j][half * 2 + q]);
+          const float val = acc[j][half * 2 + q];
+          static_cast<bf16*>(out)[static_cast<size_t>(ungated ? i : dst_row[r]) * N + col] =
+              __float2bfloat16_rn(ungated ? relu_squared(val) : val);
         }
       }
     }
@@ -409,7 +502,7 @@ __global__ void __launch_bounds__(128)
     moe_gemm_few_kernel(const bf16* __restrict__ a, long long ld_a, const bf16* __restrict__ w,
                         const int* __restrict__ perm, const int* __restrict__ offsets,
                         const int* __restrict__ tile_start, int E, int top, int K, int N, float limit, float alpha,
-                        float shift, bf16* __restrict__ out) {
+                        float shift, int ungated, bf16* __restrict__ out) {
   constexpr int BROWS = UP ? 2 * kFewCols : kFewCols;
   constexpr int kStageElems = (kFewRows + BROWS) * kFewLd;
   extern __shared__ __align__(16) unsigned char few_smem[];
@@ -425,7 +518,7 @@ __global__ void __launch_bounds__(128)
   if (threadIdx.x < kFewRows) {
     const int i = row0 + threadIdx.x;
     const int p = i < row1 ? perm[i] : -1;
-    src_row[threadIdx.x] = i < row1 ? (UP ? p / top : i) : -1;
+    src_row[threadIdx.x] = i < row1 ? ((UP || ungated) ? p / top : i) : -1;
     dst_row[threadIdx.x] = p;
   }
   __syncthreads();
@@ -500,18 +593,19 @@ __global__ void __launch_bounds__(128)
           out[static_cast<size_t>(i) * N + col] =
               __float2bfloat16_rn(clamped_glu(acc[j][half * 2 + q], acc[UP ? 2 + j : j][half * 2 + q], limit, alpha, shift));
         } else {
-          out[static_cast<size_t>(dst_row[r]) * N + col] = __float2bfloat16_rn(acc[j][half * 2 + q]);
+          const float val = acc[j][half * 2 + q];
+          out[static_cast<size_t>(ungated ? i : dst_row[r]) * N + col] = __float2bfloat16_rn(ungated ? relu_squared(val) : val);
         }
       }
     }
   }
 }
 
-// out[t] = sum_j p[t, j] y[t * top + j] (+ shared[t]); y, shared and out in the storage type, the sum in float.
+// out[t] = sum_j p[t, j] y[t * top + j] (+ shared[t], times shared_gate[t] where there is one); y, shared and out in the storage type, the sum in float.
 template <typename S>
 __global__ void __launch_bounds__(256)
     moe_combine_kernel(const S* __restrict__ y, const float* __restrict__ weights, const S* __restrict__ shared,
-                       S* __restrict__ out, int D, int top) {
+                       const float* __restrict__ shared_gate, S* __restrict__ out, int D, int top) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -519,7 +613,7 @@ __global__ void __launch_bounds__(256)
     float acc = 0.f;
     for (int j = 0; j < top; ++j)
       acc += weights[static_cast<size_t>(t) * top + j] * ldf(y + (static_cast<size_t>(t) * top + j) * D + i);
-    if (shared) acc += ldf(shared + static_cast<size_t>(t) * D + i);
+    if (shared) acc += (shared_gate ? shared_gate[t] : 1.f) * ldf(shared + static_cast<size_t>(t) * D + i);
     stf(out + static_cast<size_t>(t) * D + i, acc);
   }
 }
@@ -529,8 +623,9 @@ __global__ void __launch_bounds__(256)
 namespace pmm {
 template <typename S, int TOK>
 int launch_route(const void* x, long long ld_x, const float* w, const float* bias, int* ids, float* weights, int T, int D,
-                 int E, int top, cudaStream_t stream) {
-  const size_t smem = (static_cast<size_t>(TOK) * ((D + 3) & ~3) + static_cast<size_t>(TOK) * E) * sizeof(float);
+                 int E, int top, int scored, const float* correction, int groups, int keep, float scale,
+                 const float* gate_w, float* gate_out, cudaStream_t stream) {
+  const size_t smem = (static_cast<size_t>(TOK) * ((D + 3) & ~3) + static_cast<size_t>(TOK) * E * (scored ? 3 : 1)) * sizeof(float);
   if (smem > 200 * 1024) return PMM_ERR_BAD_ARGUMENT;
   auto kern = moe_route_kernel<S, TOK>;
   if (smem > 48 * 1024) {
@@ -538,21 +633,30 @@ int launch_route(const void* x, long long ld_x, const float* w, const float* bia
     if (err != cudaSuccess) return static_cast<int>(err);
   }
   launch_pdl(kern, dim3((T + TOK - 1) / TOK), dim3(kRouteWarps * 32), smem, stream, static_cast<const S*>(x), ld_x, w, bias,
-             ids, weights, T, D, E, top);
+             ids, weights, T, D, E, top, scored, correction, groups, keep, scale, gate_w, gate_out);
   return launch_status();
 }
 }  // namespace pmm
 
+// scored == 0: the `top` largest logits, weights their softmax.  scored != 0: scores sigmoid(z); the choice runs on
+// score + correction (may be null) within the `keep` best of `groups` groups of neighbours; weights are the chosen
+// scores over their sum, times scale.
 PMM_EXPORT int pmm_moe_route(const void* x, long long ld_x, const float* w, const float* bias, int* ids, float* weights,
-                             int T, int D, int E, int top, int dtype, cudaStream_t stream) {
+                             int T, int D, int E, int top, int scored, const float* correction, int groups, int keep,
+                             float scale, const float* gate_w, float* gate_out, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (D <= 0 || E <= 0 || top <= 0 || top > E) return PMM_ERR_BAD_ARGUMENT;
+  if (D <= 0 || E <= 0 || top <= 0 || top > E || (gate_w && !gate_out)) return PMM_ERR_BAD_ARGUMENT;
+  if (scored && (groups <= 0 || E % groups || keep <= 0 || keep > groups || top > keep * (E / groups)))
+    return PMM_ERR_BAD_ARGUMENT;
   // few tokens: a block each, so that the step's few rows still spread over the GPU; many: four a block, which
   // reads the router a quarter as often
-  const bool four = T >= 512 && (static_cast<size_t>(4) * (((D + 3) & ~3) + E)) * sizeof(float) <= 96 * 1024;
+  const bool four = T >= 512 && (static_cast<size_t>(4) * (((D + 3) & ~3) + 3 * E)) * sizeof(float) <= 96 * 1024;
   PMM_DISPATCH_DTYPE(dtype, S, {
-    if (four) return pmm::launch_route<S, 4>(x, ld_x, w, bias, ids, weights, T, D, E, top, stream);
-    return pmm::launch_route<S, 1>(x, ld_x, w, bias, ids, weights, T, D, E, top, stream);
+    if (four)
+      return pmm::launch_route<S, 4>(x, ld_x, w, bias, ids, weights, T, D, E, top, scored, correction, groups, keep, scale,
+                                     gate_w, gate_out, stream);
+    return pmm::launch_route<S, 1>(x, ld_x, w, bias, ids, weights, T, D, E, top, scored, correction, groups, keep, scale,
+                                   gate_w, gate_out, stream);
   });
   return 0;
 }
@@ -581,14 +685,17 @@ PMM_EXPORT int pmm_moe_tile_rows(int tensor_cores) {
   return tensor_cores == 2 ? pmm::kFewRows : tensor_cores ? pmm::kMmaRows : pmm::kGenRows;
 }
 
-// up != 0: a = x [T, K] (ld_a), w [E, 2N, K], out act [A, N] (storage type).  up == 0: a = act [A, K], w [E, N, K],
-// out y [A, N] in the storage type.  tensor_cores != 0 needs bfloat16, K % 8 == 0, ld_a % 8 == 0 and 16-byte aligned a, w; the
+// up == 1: a = x [T, K] (ld_a), w [E, 2N, K], out act [A, N] (storage type).  up == 0: a = act [A, K], w [E, N, K],
+// out y [A, N] in the storage type.  up == 2 (ungated experts): a = x [T, K], w [E, N, K], out act [A, N] = max(x W^T, 0)^2
+// in the order of the sorted pairs.  tensor_cores != 0 needs bfloat16, K % 8 == 0, ld_a % 8 == 0 and 16-byte aligned a, w; the
 // plan must have been made with pmm_moe_tile_rows(tensor_cores) rows a tile.
 PMM_EXPORT int pmm_moe_gemm(const void* a, long long ld_a, const void* w, const int* perm, const int* offsets,
                             const int* tile_start, int A, int E, int top, int K, int N, int up, float limit, float alpha,
                             float shift, void* out, int tensor_cores, int dtype, cudaStream_t stream) {
   if (A <= 0) return 0;
-  if (E <= 0 || top <= 0 || K <= 0 || N <= 0) return PMM_ERR_BAD_ARGUMENT;
+  if (E <= 0 || top <= 0 || K <= 0 || N <= 0 || up < 0 || up > 2) return PMM_ERR_BAD_ARGUMENT;
+  const int ungated = up == 2 ? 1 : 0;
+  if (ungated) up = 0;
   const int tile_rows = pmm_moe_tile_rows(tensor_cores);
   const int row_tiles = A / tile_rows + (E < A ? E : A);
   if (row_tiles > 65535) return PMM_ERR_BAD_ARGUMENT;
@@ -607,45 +714,46 @@ PMM_EXPORT int pmm_moe_gemm(const void* a, long long ld_a, const void* w, const 
         if (err != cudaSuccess) return static_cast<int>(err);
         pmm::launch_pdl(kern, grid, dim3(128), smem, stream, static_cast<const pmm::bf16*>(a), ld_a,
                         static_cast<const pmm::bf16*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift,
-                        static_cast<pmm::bf16*>(out));
+                        ungated, static_cast<pmm::bf16*>(out));
       } else {
         auto kern = pmm::moe_gemm_few_kernel<false>;
         err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (err != cudaSuccess) return static_cast<int>(err);
         pmm::launch_pdl(kern, grid, dim3(128), smem, stream, static_cast<const pmm::bf16*>(a), ld_a,
                         static_cast<const pmm::bf16*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift,
-                        static_cast<pmm::bf16*>(out));
+                        ungated, static_cast<pmm::bf16*>(out));
       }
       return pmm::launch_status();
     }
     const dim3 grid((N + pmm::kMmaCols - 1) / pmm::kMmaCols, row_tiles);
     if (up)
       pmm::launch_pdl(pmm::moe_gemm_mma_kernel<true>, grid, dim3(128), 0, stream, static_cast<const pmm::bf16*>(a), ld_a,
-                      static_cast<const pmm::bf16*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift, out);
+                      static_cast<const pmm::bf16*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift, ungated, out);
     else
       pmm::launch_pdl(pmm::moe_gemm_mma_kernel<false>, grid, dim3(128), 0, stream, static_cast<const pmm::bf16*>(a), ld_a,
-                      static_cast<const pmm::bf16*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift, out);
+                      static_cast<const pmm::bf16*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift, ungated, out);
     return pmm::launch_status();
   }
   const dim3 grid((N + pmm::kGenCols - 1) / pmm::kGenCols, row_tiles);
   PMM_DISPATCH_DTYPE(dtype, S, {
     if (up)
       pmm::launch_pdl(pmm::moe_gemm_generic_kernel<S, true>, grid, dim3(256), 0, stream, static_cast<const S*>(a), ld_a,
-                      static_cast<const S*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift, out);
+                      static_cast<const S*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift, ungated, out);
     else
       pmm::launch_pdl(pmm::moe_gemm_generic_kernel<S, false>, grid, dim3(256), 0, stream, static_cast<const S*>(a), ld_a,
-                      static_cast<const S*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift, out);
+                      static_cast<const S*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift, ungated, out);
   });
   return pmm::launch_status();
 }
 
-PMM_EXPORT int pmm_moe_combine(const void* y, const float* weights, const void* shared, void* out, int T, int D, int top,
-                               int dtype, cudaStream_t stream) {
+PMM_EXPORT int pmm_moe_combine(const void* y, const float* weights, const void* shared, const float* shared_gate, void* out,
+                               int T, int D, int top, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (D <= 0 || top <= 0) return PMM_ERR_BAD_ARGUMENT;
   int ytiles = (D + 1023) / 1024;
   if (ytiles > 64) ytiles = 64;
   PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::moe_combine_kernel<S>, dim3(T, ytiles), dim3(256), 0, stream,
-                                               static_cast<const S*>(y), weights, static_cast<const S*>(shared), static_cast<S*>(out), D, top));
+                                               static_cast<const S*>(y), weights, static_cast<const S*>(shared), shared_gate,
+                                               static_cast<S*>(out), D, top));
   return pmm::launch_status();
 }

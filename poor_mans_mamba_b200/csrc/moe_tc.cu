@@ -49,7 +49,8 @@ template <bool UP>
 __global__ void __launch_bounds__(kGThreads)
     moe_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                   const int* __restrict__ perm, const int* __restrict__ offsets, const int* __restrict__ tile_start, int E,
-                  int K, int N, float limit, float alpha, float shift, void* __restrict__ out, int* __restrict__ status) {
+                  int K, int N, float limit, float alpha, float shift, int ungated, void* __restrict__ out,
+                  int* __restrict__ status) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ unsigned char smem_raw[];
@@ -182,7 +183,8 @@ __global__ void __launch_bounds__(kGThreads)
           }
         }
       } else {
-        bf16* dst_row = static_cast<bf16*>(out) + static_cast<size_t>(row_ok ? perm[i] : 0) * N;
+        // (ungated experts' up product: rows stay in the order of the sorted pairs, values become max(z, 0)^2)
+        bf16* dst_row = static_cast<bf16*>(out) + static_cast<size_t>(row_ok ? (ungated ? i : perm[i]) : 0) * N;
 #pragma unroll 1
         for (int q = 0; q < kGN / 32; ++q) {
           unsigned v[32];
@@ -196,8 +198,14 @@ __global__ void __launch_bounds__(kGThreads)
                 uint4 pack;
                 __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pack);
 #pragma unroll
-                for (int h = 0; h < 4; ++h)
-                  p2[h] = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * h]), __uint_as_float(v[j + 2 * h + 1]));
+                for (int h = 0; h < 4; ++h) {
+                  float v0 = __uint_as_float(v[j + 2 * h]), v1 = __uint_as_float(v[j + 2 * h + 1]);
+                  if (ungated) {
+                    v0 = fmaxf(v0, 0.f), v1 = fmaxf(v1, 0.f);
+                    v0 *= v0, v1 *= v1;
+                  }
+                  p2[h] = __floats2bfloat162_rn(v0, v1);
+                }
                 *reinterpret_cast<uint4*>(dst_row + col) = pack;
               }
             }
@@ -267,7 +275,9 @@ PMM_EXPORT int pmm_moe_tc_gemm(const void* a, long long ld_a, const void* w, con
                                const int* tile_start, int A, int E, int K, int N, int up, float limit, float alpha,
                                float shift, void* out, int* status, cudaStream_t stream) {
   if (A <= 0) return 0;
-  if (E <= 0 || !pmm_moe_tc_supported(K, N, ld_a) || !status) return PMM_ERR_BAD_ARGUMENT;
+  if (E <= 0 || !pmm_moe_tc_supported(K, N, ld_a) || !status || up < 0 || up > 2) return PMM_ERR_BAD_ARGUMENT;
+  const int ungated = up == 2 ? 1 : 0;  // up == 2: w [E * N, K], out = max(a W^T, 0)^2 in the order of the sorted pairs
+  if (ungated) up = 0;
   if (reinterpret_cast<uintptr_t>(a) % 16 || reinterpret_cast<uintptr_t>(w) % 16 || reinterpret_cast<uintptr_t>(out) % 16)
     return PMM_ERR_BAD_ARGUMENT;
   CUtensorMap map_a, map_w;
@@ -283,13 +293,13 @@ PMM_EXPORT int pmm_moe_tc_gemm(const void* a, long long ld_a, const void* w, con
     err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pmm::kGSmem));
     if (err != cudaSuccess) return static_cast<int>(err);
     pmm::launch_pdl(kern, grid, dim3(pmm::kGThreads), pmm::kGSmem, stream, map_a, map_w, perm, offsets, tile_start, E, K, N,
-                    limit, alpha, shift, out, status);
+                    limit, alpha, shift, ungated, out, status);
   } else {
     auto kern = pmm::moe_tc_kernel<false>;
     err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pmm::kGSmem));
     if (err != cudaSuccess) return static_cast<int>(err);
     pmm::launch_pdl(kern, grid, dim3(pmm::kGThreads), pmm::kGSmem, stream, map_a, map_w, perm, offsets, tile_start, E, K, N,
-                    limit, alpha, shift, out, status);
+                    limit, alpha, shift, ungated, out, status);
   }
   return pmm::launch_status();
 }

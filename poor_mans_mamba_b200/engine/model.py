@@ -45,6 +45,11 @@ class Model:
             if not 0 <= call.layer < len(self.layers):
                 raise ValueError(f"execution order names a layer that does not exist: {call}")
         self.final_norm = build_part("norm", spec.final_norm, width=spec.hidden_size)
+        self.reentry = None
+        if spec.reentry is not None:
+            self.reentry = build_part("stream_update", spec.reentry, hidden_size=spec.hidden_size)
+        elif any(call.enters for call in spec.order):
+            raise ValueError("the execution order re-enters the stream but the model has no reentry part")
         self.embedding: Optional[Tensor] = None
         self.head: Optional[Tensor] = None
         self.dtype: Optional[torch.dtype] = None
@@ -61,10 +66,14 @@ class Model:
             for part in layer.parts():
                 out.append((f"{layer.prefix}{part.name}", part))
         out.append((self.spec.final_norm.name, self.final_norm))
+        if self.reentry is not None:
+            out.append((self.spec.reentry.name, self.reentry))
         return out
 
     @staticmethod
     def _full_name(prefix: str, name: str) -> str:
+        if name.startswith("/"):
+            return name[1:]  # a tensor shared by parts of several layers, named in full
         return f"{prefix}.{name}" if name else prefix
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -95,6 +104,8 @@ class Model:
         for layer in self.layers:
             layer.finalize(dtype, self.device)
         self.final_norm.finalize(dtype, self.device)
+        if self.reentry is not None:
+            self.reentry.finalize(dtype, self.device)
 
     # ------------------------------------------------------------------ state
     def state_specs(self) -> Dict[int, List[Tuple[str, StateSpec]]]:
@@ -122,6 +133,9 @@ class Model:
         h = ws.alloc((T, D), torch.float32)
         K.embed(h, self.embedding, ctx.tokens, self.spec.embedding_multiplier)
         stream = ResidualStream(h, ctx, self._branch_buffers, lanes=self.spec.residual_lanes)
+        if self.reentry is not None:
+            stream.reentry = ws.alloc((T, 2 * D), ctx.dtype)
+            K.cast_rows(h, [], stream.reentry[:, D:])
         order = self.spec.order
         # Fetching the next layer's weights beside a layer's products pays where the mixers' phase is
         # long enough to cover it and the products still wait for their weights: measured on the 0.5B
@@ -134,6 +148,9 @@ class Model:
             layer = self.layers[call.layer]
             if ctx.unjoined_stream is not None and not getattr(layer, "joins_side_stream", lambda c: False)(ctx):
                 self._join(ctx, h.device)
+            if call.enters:
+                self._join(ctx, h.device)
+                self.reentry.forward(stream, ctx)
             layer.forward(stream, ctx, caches[call.cache_of])
         ctx.fetch_ahead = None
         self._join(ctx, h.device)

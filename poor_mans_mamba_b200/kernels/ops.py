@@ -119,17 +119,29 @@ _SIGNATURES = {
                          c_int, c_int, c_void_p],
     "pmm_clamped_glu": [c_void_p, c_longlong, c_float, c_float, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_moe_route": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                      c_void_p],
+                      c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p],
     "pmm_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "pmm_moe_tile_rows": [c_int],
     "pmm_moe_gemm": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                      c_int, c_float, c_float, c_float, c_void_p, c_int, c_int, c_void_p],
-    "pmm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_moe_tc_tile_rows": [],
     "pmm_moe_tc_supported": [c_int, c_int, c_longlong],
     "pmm_moe_gather_rows": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
     "pmm_moe_tc_gemm": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                         c_float, c_float, c_float, c_void_p, c_void_p, c_void_p],
+    "pmm_latent_norm_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_int, c_void_p],
+    "pmm_latent_query_rot": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_void_p],
+    "pmm_head_gate": [c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                      c_void_p],
+    "pmm_token_gated_update_fits": [c_int, c_int],
+    "pmm_token_gated_update": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p, c_longlong, c_int,
+                               c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_cast_rows": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
+    "pmm_relu_squared": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
     "pmm_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                         c_void_p, c_void_p, c_void_p],
 }
@@ -1437,21 +1449,175 @@ def clamped_glu(gate_up: Tensor, limit: float, alpha: float, shift: float, out: 
           float(shift), out.data_ptr(), T, F2 // 2, _dt(out), _stream())
 
 
+# ----------------------------------------------------------------------------- latent attention
+def latent_padded_dim(kv_rank: int, rot_dim: int) -> int:
+    """The head size the attention kernels see for a latent of ``kv_rank`` entries and a rotated key part of
+    ``rot_dim``: the next of 16, 32, 64, 128 (the sizes the tensor-core kernels take), beyond that a multiple of 16."""
+    need = kv_rank + rot_dim
+    for d in (16, 32, 64, 128):
+        if need <= d:
+            return d
+    return (need + 15) // 16 * 16
+
+
+def latent_norm_store(q_lat: Tensor, kv_lat: Tensor, q_w: Tensor, kv_w: Tensor, eps: float, inv_freq: Optional[Tensor],
+                      positions: Tensor, seq_of: Tensor, block_table: Tensor, pool: Tensor, cq: Tensor, kv_rank: int,
+                      rot_dim: int, rot_dims: int) -> None:
+    """cq = rms(q_lat) * q_w; the cache rows of the step's tokens: key row [rms(kv_lat[:kv_rank]) * kv_w | the last
+    rot_dim entries of kv_lat, of which the first rot_dims turn in neighbouring pairs | 0], value row [the normed
+    latent | 0], into ``pool`` [pages, 2, page_size, Dp].  Norms, angles, sines and cosines are float."""
+    _cuda(q_lat, kv_lat, q_w, kv_w, inv_freq, positions, seq_of, block_table, pool, cq)
+    T, q_rank = q_lat.shape
+    if not (kv_lat.shape == (T, kv_rank + rot_dim) and q_lat.dtype == kv_lat.dtype == pool.dtype == cq.dtype
+            and q_lat.stride(1) == 1 and kv_lat.stride(1) == 1):
+        raise KernelError("latent_norm_store: q_lat [T, q_rank], kv_lat [T, kv_rank + rot_dim] of the pool's type")
+    if not (cq.shape == (T, q_rank) and cq.is_contiguous()):
+        raise KernelError("latent_norm_store: cq must be contiguous [T, q_rank]")
+    if not (pool.dim() == 4 and pool.shape[1] == 2 and pool.is_contiguous() and pool.shape[3] >= kv_rank + rot_dim):
+        raise KernelError("latent_norm_store: pool must be contiguous [pages, 2, page_size, Dp >= kv_rank + rot_dim]")
+    _f32vec(q_w, q_rank, "latent_norm_store: q_w")
+    _f32vec(kv_w, kv_rank, "latent_norm_store: kv_w")
+    _f32vec(inv_freq, rot_dims // 2, "latent_norm_store: inv_freq")
+    _i32(positions, "latent_norm_store: positions")
+    _i32(seq_of, "latent_norm_store: seq_of")
+    _i32(block_table, "latent_norm_store: block_table")
+    _call("pmm_latent_norm_store", q_lat.data_ptr(), q_lat.stride(0), kv_lat.data_ptr(), kv_lat.stride(0), q_w.data_ptr(),
+          kv_w.data_ptr(), float(eps), _ptr(inv_freq), positions.data_ptr(), seq_of.data_ptr(), block_table.data_ptr(),
+          block_table.shape[1], pool.data_ptr(), pool.shape[2], cq.data_ptr(), T, q_rank, int(kv_rank), int(rot_dim),
+          int(rot_dims), pool.shape[3], _dt(q_lat), _stream())
+
+
+def latent_query_rot(q: Tensor, inv_freq: Optional[Tensor], positions: Tensor, q_out: Tensor, heads: int, dim: int,
+                     rot_dim: int, rot_dims: int, kv_rank: int, padded_dim: int) -> None:
+    """q [T, heads * (dim + rot_dim)]: the rotated part of every head turns and goes to q_out[t, h, kv_rank ..
+    kv_rank + rot_dim); the entries from there to padded_dim become zero; the first kv_rank stay as they are."""
+    _cuda(q, inv_freq, positions, q_out)
+    T = q.shape[0]
+    if not (q.shape[1] == heads * (dim + rot_dim) and q.stride(1) == 1 and q.dtype == q_out.dtype
+            and q_out.shape == (T, heads * padded_dim) and q_out.is_contiguous()):
+        raise KernelError("latent_query_rot: q [T, H * (dim + rot_dim)], q_out contiguous [T, H * Dp] of one type")
+    _f32vec(inv_freq, rot_dims // 2, "latent_query_rot: inv_freq")
+    _i32(positions, "latent_query_rot: positions")
+    _call("pmm_latent_query_rot", q.data_ptr(), q.stride(0), _ptr(inv_freq), positions.data_ptr(), q_out.data_ptr(), T,
+          int(heads), int(dim), int(rot_dim), int(rot_dims), int(kv_rank), int(padded_dim), _dt(q), _stream())
+
+
+def head_gate(a: Tensor, g: Optional[Tensor], scale: float, out: Tensor, heads: int, vdim: int) -> None:
+    """out[t, h * vdim + i] = scale * a[t, h * vdim + i] * sigmoid(g[t, h]) (g None: scale only)."""
+    _cuda(a, g, out)
+    T = a.shape[0]
+    if not (a.shape == (T, heads * vdim) and out.shape == a.shape and a.stride(1) == 1 and out.stride(1) == 1
+            and a.dtype == out.dtype):
+        raise KernelError("head_gate: a and out [T, H * vdim] of one type")
+    if g is not None and not (g.shape == (T, heads) and g.stride(1) == 1 and g.dtype == a.dtype):
+        raise KernelError("head_gate: g [T, H] of a's type")
+    _call("pmm_head_gate", a.data_ptr(), a.stride(0), _ptr(g), g.stride(0) if g is not None else 0, float(scale),
+          out.data_ptr(), out.stride(0), T, int(heads), int(vdim), _dt(a), _stream())
+
+
+def head_linear(x: Tensor, w: Tensor, out: Tensor) -> None:
+    """out[t, h, :] = x[t, h, :] @ w[h]: a product per head, x [T, H, K] and out [T, H, N] views with unit inner
+    stride, w [H, K, N] (any strides the library takes).  Float32 operands stay true float32."""
+    _cuda(x, w, out)
+    H = w.shape[0]
+    if not (x.dim() == 3 and out.dim() == 3 and x.shape[1] == H and out.shape[1] == H and x.shape[2] == w.shape[1]
+            and out.shape[2] == w.shape[2] and x.shape[0] == out.shape[0] and x.stride(2) == 1 and out.stride(2) == 1
+            and x.dtype == w.dtype == out.dtype):
+        raise KernelError("head_linear: x [T, H, K], w [H, K, N], out [T, H, N] of one type")
+    if x.shape[0] == 0:
+        return
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        torch.bmm(x.transpose(0, 1), w, out=out.transpose(0, 1))
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+# ----------------------------------------------------------------------------- updates of the residual stream
+def token_gated_update_fits(width: int, rank: int) -> bool:
+    return bool(_fn("pmm_token_gated_update_fits")(int(width), int(rank)))
+
+
+def token_gated_update(h: Tensor, branches: Sequence[Tuple[Tensor, float]], tokens: Tensor, table: Tensor, col0: int,
+                       w_gate: Tensor, w_proj: Tensor, norm_w: Tensor, eps: float) -> None:
+    """h <- x + rms(Wp (gelu_tanh(Wg x) * e)) * norm_w with x = h + sum(scale_i * branch_i) (at most two branches)
+    and e = table[token, col0 : col0 + R]; h [T, D] float32 in place, Wg [R, D], Wp [D, R]."""
+    items = list(branches)
+    _cuda(h, tokens, table, w_gate, w_proj, norm_w, *[b for b, _ in items])
+    T, D = h.shape
+    R = w_gate.shape[0]
+    if not (h.dtype == torch.float32 and h.is_contiguous() and len(items) <= 2):
+        raise KernelError("token_gated_update: h contiguous float32 and at most two branches")
+    if not (w_gate.shape == (R, D) and w_proj.shape == (D, R) and w_gate.is_contiguous() and w_proj.is_contiguous()
+            and w_gate.dtype == w_proj.dtype == table.dtype and table.dim() == 2 and table.stride(1) == 1
+            and 0 <= col0 and col0 + R <= table.shape[1]):
+        raise KernelError("token_gated_update: Wg [R, D], Wp [D, R] and the table of one type, the columns inside it")
+    for b, _ in items:
+        if not (b.shape == h.shape and b.is_contiguous() and b.dtype == w_gate.dtype):
+            raise KernelError("token_gated_update: branches contiguous [T, D] of the matrices' type")
+    if not token_gated_update_fits(D, R):
+        raise KernelError("token_gated_update: a token's rows do not fit the shared memory")
+    _f32vec(norm_w, D, "token_gated_update: norm_w")
+    _i32(tokens, "token_gated_update: tokens")
+    (a, sa), (b, sb) = (items + [(None, 0.0), (None, 0.0)])[:2]
+    _call("pmm_token_gated_update", h.data_ptr(), _ptr(a), float(sa), _ptr(b), float(sb), tokens.data_ptr(), table.data_ptr(),
+          table.stride(0), int(col0), w_gate.data_ptr(), w_proj.data_ptr(), norm_w.data_ptr(), float(eps), T, D, R,
+          _dt(w_gate), _stream())
+
+
+def cast_rows(h: Tensor, branches: Sequence[Tuple[Tensor, float]], out: Tensor) -> None:
+    """h <- h + sum(scale_i * branch_i) (at most two), out[t, :D] = h[t] in out's type (out may be a column block)."""
+    items = list(branches)
+    _cuda(h, out, *[b for b, _ in items])
+    T, D = h.shape
+    if not (h.dtype == torch.float32 and h.is_contiguous() and out.shape == (T, D) and out.stride(1) == 1 and len(items) <= 2):
+        raise KernelError("cast_rows: h contiguous float32 [T, D], out [T, D] with unit inner stride, at most two branches")
+    for b, _ in items:
+        if not (b.shape == h.shape and b.is_contiguous() and b.dtype == out.dtype):
+            raise KernelError("cast_rows: branches contiguous [T, D] of out's type")
+    (a, sa), (b, sb) = (items + [(None, 0.0), (None, 0.0)])[:2]
+    _call("pmm_cast_rows", h.data_ptr(), _ptr(a), float(sa), _ptr(b), float(sb), out.data_ptr(), out.stride(0), T, D,
+          _dt(out), _stream())
+
+
+def relu_squared(x: Tensor, out: Tensor) -> None:
+    """out = max(x, 0)^2, element-wise over [T, F] (rows may be strided)."""
+    _cuda(x, out)
+    if not (x.dim() == 2 and out.shape == x.shape and x.stride(1) == 1 and out.stride(1) == 1 and x.dtype == out.dtype):
+        raise KernelError("relu_squared: x and out [T, F] of one type with unit inner stride")
+    _call("pmm_relu_squared", x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), x.shape[0], x.shape[1], _dt(x),
+          _stream())
+
+
 # ----------------------------------------------------------------------------- routed feed-forward
-def moe_route(x: Tensor, router_w: Tensor, router_b: Optional[Tensor], top: int, ids: Tensor, weights: Tensor) -> None:
-    """ids, weights [T, top]: the ``top`` largest of x Wr^T + br (float arithmetic) and their softmax."""
-    _cuda(x, router_w, router_b, ids, weights)
+def moe_route(x: Tensor, router_w: Tensor, router_b: Optional[Tensor], top: int, ids: Tensor, weights: Tensor,
+              scored: bool = False, correction: Optional[Tensor] = None, groups: int = 1, keep: int = 1,
+              scale: float = 1.0, gate_w: Optional[Tensor] = None, gate_out: Optional[Tensor] = None) -> None:
+    """ids, weights [T, top] of z = x Wr^T + br (float arithmetic).  Plain: the ``top`` largest z and their softmax.
+    ``scored``: s = sigmoid(z); the ``top`` largest of s + correction among the experts of the ``keep`` groups (of
+    ``groups`` equal groups of neighbours) whose two largest s + correction sum highest; weights the chosen s over
+    their sum, times ``scale``.  ``gate_w`` [D] float32: gate_out[t] = sigmoid(x[t] . gate_w) as well."""
+    _cuda(x, router_w, router_b, ids, weights, correction, gate_w, gate_out)
     T, D = x.shape
     E = router_w.shape[0]
     if not (router_w.shape == (E, D) and router_w.dtype == torch.float32 and router_w.is_contiguous()):
         raise KernelError("moe_route: router weight [E, D] float32")
     if router_b is not None:
         _f32vec(router_b, E, "moe_route: router bias")
+    _f32vec(correction, E, "moe_route: correction")
     if not (ids.shape == (T, top) and ids.dtype == torch.int32 and ids.is_contiguous() and weights.shape == (T, top)
             and weights.dtype == torch.float32 and weights.is_contiguous() and 1 <= top <= E):
         raise KernelError("moe_route: ids int32 and weights float32, both contiguous [T, top], top <= experts")
+    if scored and not (groups >= 1 and E % groups == 0 and 1 <= keep <= groups and top <= keep * (E // groups)):
+        raise KernelError("moe_route: groups must divide the experts, keep <= groups, top <= keep * experts / groups")
+    if gate_w is not None:
+        _f32vec(gate_w, D, "moe_route: gate_w")
+        if not (gate_out is not None and gate_out.dtype == torch.float32 and gate_out.is_contiguous() and gate_out.numel() == T):
+            raise KernelError("moe_route: gate_out must be contiguous float32 [T]")
     _call("pmm_moe_route", x.data_ptr(), _rows_view(x, "moe_route"), router_w.data_ptr(), _ptr(router_b), ids.data_ptr(),
-          weights.data_ptr(), T, D, E, int(top), _dt(x), _stream())
+          weights.data_ptr(), T, D, E, int(top), int(bool(scored)), _ptr(correction), int(groups), int(keep), float(scale),
+          _ptr(gate_w), _ptr(gate_out) if gate_w is not None else None, _dt(x), _stream())
 
 
 _MOE_FORMS = {"float": 0, "mma": 1, "mma_few": 2}
@@ -1499,21 +1665,23 @@ def moe_gather_rows(x: Tensor, perm: Tensor, top: int, out: Tensor) -> None:
 
 
 def moe_tc_gemm(a: Tensor, w: Tensor, perm: Tensor, offsets: Tensor, tile_start: Tensor, up: bool, out: Tensor,
-                limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0) -> None:
+                limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0, ungated: bool = False) -> None:
     """The grouped product on the fifth-generation tensor cores.  a [pairs, K]: rows in the order of the sorted
     pairs (the gathered token rows, or the activation); w [E, N (2N), K]; the plan made for "tcgen05" row tiles.
     ``up``: out = act [pairs, N] with the clamped gated activation; else out = y [pairs, N] in the order of the
-    pairs (both bfloat16)."""
+    pairs (both bfloat16).  ``up`` and ``ungated``: w [E, N, K], out = act [pairs, N] = max(a W^T, 0)^2."""
     _cuda(a, w, perm, offsets, tile_start, out)
     A, Kd = a.shape
     E, N = w.shape[0], out.shape[1]
-    if not (w.dim() == 3 and w.is_contiguous() and w.shape == (E, (2 if up else 1) * N, Kd) and perm.numel() == A
+    if ungated and not up:
+        raise KernelError("moe_tc_gemm: only an up product is gated or ungated")
+    if not (w.dim() == 3 and w.is_contiguous() and w.shape == (E, (2 if up and not ungated else 1) * N, Kd) and perm.numel() == A
             and out.shape == (A, N) and out.is_contiguous() and out.dtype == torch.bfloat16
             and offsets.numel() == E + 1 and tile_start.numel() == E + 1 and moe_tc_supported(a, w, N)):
         raise KernelError("moe_tc_gemm: operands outside what the kernel takes")
     _call("pmm_moe_tc_gemm", a.data_ptr(), a.stride(0), w.data_ptr(), perm.data_ptr(), offsets.data_ptr(),
-          tile_start.data_ptr(), A, E, Kd, N, int(bool(up)), float(limit), float(alpha), float(shift), out.data_ptr(),
-          _tc_status(a.device).data_ptr(), _stream())
+          tile_start.data_ptr(), A, E, Kd, N, (2 if ungated else 1) if up else 0, float(limit), float(alpha), float(shift),
+          out.data_ptr(), _tc_status(a.device).data_ptr(), _stream())
 
 
 def moe_gemm_tc_ok(a: Tensor, w: Tensor) -> bool:
@@ -1523,16 +1691,19 @@ def moe_gemm_tc_ok(a: Tensor, w: Tensor) -> bool:
 
 
 def moe_gemm(a: Tensor, w: Tensor, perm: Tensor, offsets: Tensor, tile_start: Tensor, top: int, up: bool, out: Tensor,
-             form: str, limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0) -> None:
+             form: str, limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0, ungated: bool = False) -> None:
     """Grouped product over the rows of a plan.  ``up``: a = x [T, K], w [E, 2N, K] ([gate | up] rows of
     every expert), out = act [T*top, N] in the storage type, with the clamped gated activation.  Else:
-    a = act [T*top, K], w [E, N, K], out = y [T*top, N] in the order of the pairs."""
+    a = act [T*top, K], w [E, N, K], out = y [T*top, N] in the order of the pairs.  ``up`` and ``ungated``: w [E, N, K],
+    out = act [T*top, N] = max(x W^T, 0)^2."""
     _cuda(a, w, perm, offsets, tile_start, out)
     A = perm.numel()
     E = w.shape[0]
     K = a.shape[1]
     N = out.shape[1]
-    if not (w.dim() == 3 and w.is_contiguous() and w.shape == (E, (2 if up else 1) * N, K) and w.dtype == a.dtype):
+    if ungated and not up:
+        raise KernelError("moe_gemm: only an up product is gated or ungated")
+    if not (w.dim() == 3 and w.is_contiguous() and w.shape == (E, (2 if up and not ungated else 1) * N, K) and w.dtype == a.dtype):
         raise KernelError("moe_gemm: w must be contiguous [E, N (2N for the gate and up rows), K] of a's type")
     if not (out.shape == (A, N) and out.is_contiguous() and out.dtype == a.dtype):
         raise KernelError("moe_gemm: out [pairs, N] of the operands' type")
@@ -1542,13 +1713,14 @@ def moe_gemm(a: Tensor, w: Tensor, perm: Tensor, offsets: Tensor, tile_start: Te
     if tensor_cores and not moe_gemm_tc_ok(a, w):
         raise KernelError("moe_gemm: the tensor-core forms need bfloat16, K a multiple of 8 and 16-byte aligned rows")
     _call("pmm_moe_gemm", a.data_ptr(), _rows_view(a, "moe_gemm"), w.data_ptr(), perm.data_ptr(), offsets.data_ptr(),
-          tile_start.data_ptr(), A, E, int(top), K, N, int(bool(up)), float(limit), float(alpha), float(shift),
-          out.data_ptr(), tensor_cores, _dt(a), _stream())
+          tile_start.data_ptr(), A, E, int(top), K, N, (2 if ungated else 1) if up else 0, float(limit), float(alpha),
+          float(shift), out.data_ptr(), tensor_cores, _dt(a), _stream())
 
 
-def moe_combine(y: Tensor, weights: Tensor, shared: Optional[Tensor], out: Tensor) -> None:
-    """out[t] = sum_j weights[t, j] * y[t*top + j] (+ shared[t])."""
-    _cuda(y, weights, shared, out)
+def moe_combine(y: Tensor, weights: Tensor, shared: Optional[Tensor], out: Tensor,
+                shared_gate: Optional[Tensor] = None) -> None:
+    """out[t] = sum_j weights[t, j] * y[t*top + j] (+ shared[t], times shared_gate[t] where given)."""
+    _cuda(y, weights, shared, out, shared_gate)
     T, top = weights.shape
     D = out.shape[1]
     if not (y.shape == (T * top, D) and y.dtype == out.dtype and y.is_contiguous() and out.shape == (T, D)
@@ -1556,7 +1728,11 @@ def moe_combine(y: Tensor, weights: Tensor, shared: Optional[Tensor], out: Tenso
         raise KernelError("moe_combine: y [T*top, D] of out's type, weights [T, top] float32, out contiguous [T, D]")
     if shared is not None and not (shared.shape == (T, D) and shared.is_contiguous() and shared.dtype == out.dtype):
         raise KernelError("moe_combine: shared must be contiguous [T, D] of out's type")
-    _call("pmm_moe_combine", y.data_ptr(), weights.data_ptr(), _ptr(shared), out.data_ptr(), T, D, top, _dt(out), _stream())
+    if shared_gate is not None and not (shared is not None and shared_gate.dtype == torch.float32
+                                        and shared_gate.is_contiguous() and shared_gate.numel() == T):
+        raise KernelError("moe_combine: shared_gate must be contiguous float32 [T] beside a shared output")
+    _call("pmm_moe_combine", y.data_ptr(), weights.data_ptr(), _ptr(shared), _ptr(shared_gate), out.data_ptr(), T, D, top,
+          _dt(out), _stream())
 
 
 def add_row_bias_(x: Tensor, bias: Tensor) -> None:

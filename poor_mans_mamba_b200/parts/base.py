@@ -21,7 +21,8 @@ Tensor = torch.Tensor
 # ----------------------------------------------------------------------------- tensors a part needs
 @dataclass(frozen=True)
 class ParamSpec:
-    """One tensor of a part.  ``name`` is relative to the part's prefix.
+    """One tensor of a part.  ``name`` is relative to the part's prefix; a name that starts with "/" is the
+    tensor's full name (a table that the parts of several layers share: each declares it, it is loaded once).
 
     kind: "matrix"  -> kept in the compute type (bfloat16 or float32);
           "vector"  -> always float32 on the device (norm weights, biases, per-head scalars);
@@ -232,6 +233,15 @@ class FeedForward(Part):
         return []
 
 
+class StreamUpdate(Part):
+    """Changes the residual stream in place at the end of a layer, reading nothing but the stream and the
+    step's tokens (a per-token input, for instance): forward(stream, ctx), with ``stream`` the
+    ResidualStream, whose waiting branches the part folds in first."""
+
+    def forward(self, stream, ctx) -> None:
+        raise NotImplementedError
+
+
 # ----------------------------------------------------------------------------- specs (data)
 @dataclass(frozen=True)
 class PartSpec:
@@ -259,9 +269,11 @@ class LayerSpec:
 @dataclass(frozen=True)
 class LayerCall:
     """One entry of the execution order: run ``layer`` on the cache of ``cache_of``
-    (its own unless it reads another layer's)."""
+    (its own unless it reads another layer's).  ``enters``: the model's ``reentry`` part
+    changes the stream right before this call."""
     layer: int
     cache_of: int
+    enters: bool = False
 
 
 @dataclass(frozen=True)
@@ -277,6 +289,10 @@ class ModelSpec:
     head_multiplier: float
     eos_token_id: int = -1
     bos_token_id: int = 0
+    # A stream update (`register_stream_update`) that runs before every call of the order with ``enters``.
+    # With one, the embedding's output is kept for the whole step (in the storage type, as the right half
+    # of ``ResidualStream.reentry`` [T, 2D]; the left half is the part's scratch).
+    reentry: Optional[PartSpec] = None
     # None: one residual stream [T, D].  n >= 1: the residual state is n lanes [n, T, D], all equal to
     # the embedding's output at the start and summed before the final norm (arrangements that mix
     # lanes, such as ``hyper_prenorm``, read and write them through the ResidualStream)
@@ -285,7 +301,7 @@ class ModelSpec:
 
 # ----------------------------------------------------------------------------- registries
 _REGISTRIES: Dict[str, Dict[str, Callable[..., Part]]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "arrangement": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "arrangement": {}, "stream_update": {},
 }
 
 
@@ -314,6 +330,10 @@ def register_position_encoding(kind: str, factory: Callable[..., PositionEncodin
 
 def register_arrangement(kind: str, factory: Callable[..., Any]) -> None:
     _register("arrangement", kind, factory)
+
+
+def register_stream_update(kind: str, factory: Callable[..., "StreamUpdate"]) -> None:
+    _register("stream_update", kind, factory)
 
 
 def build_part(family: str, spec: PartSpec, **extra: Any) -> Any:

@@ -73,6 +73,9 @@ class ResidualStream:
         self.lanes: Optional[Tensor] = None
         self._lanes_fresh = False
         self.lane_pending: Optional[Tuple[Tensor, Tensor, Tensor]] = None
+        # [T, 2D] in the storage type where the model keeps the embedding's output (ModelSpec.keeps_embedding):
+        # the right half holds it, the left half is scratch for the arrangement that uses it
+        self.reentry: Optional[Tensor] = None
         if lanes is not None:
             self.lanes = ctx.workspace.alloc((int(lanes),) + tuple(h.shape), torch.float32)
             self._lanes_fresh = True
@@ -149,6 +152,19 @@ class ResidualStream:
             self.pending_post = None
             self._taken = 0
         return out
+
+    def take_pending(self, at_most: int = 2) -> List[Tuple[Tensor, float]]:
+        """Hands the waiting branches (at most ``at_most``; the surplus and a waiting post norm are settled
+        first) to a launch that folds them into the stream itself; the stream then holds none."""
+        if self.lanes is not None:
+            raise RuntimeError("a residual state in lanes has no single stream to fold branches into")
+        self._settle_post()
+        while len(self.pending) > at_most:
+            fold_branches(self.h, self.pending[:2])
+            self.pending = self.pending[2:]
+        items, self.pending = self.pending, []
+        self._taken = 0
+        return items
 
     def flush(self) -> Tensor:
         if self.lanes is not None:
@@ -383,4 +399,80 @@ class ParallelPreNormBlock(Part):
         ws.release(mark)
 
 
+class SharedNormParallelBlock(Part):
+    """One norm whose output the mixer and the feed-forward both read, then the layer's stream updates:
+
+        n = norm(x);  x <- x + (mixer(n) + ffn(n));  x <- update(x) for every part of ``updates``.
+
+    Parts: "norm", "mixer", "ffn" (or None), "updates" (a tuple of stream updates, may be empty).  The
+    mixer runs on a side stream beside the feed-forward (parallel branches of a recorded step); both
+    results wait on the stream and are folded in by the launch that reads the stream next: the first
+    update, or the next layer's norm."""
+
+    def __init__(self, spec: LayerSpec, hidden_size: int):
+        self.prefix = spec.prefix
+        self.hidden_size = hidden_size
+        unknown = set(spec.parts) - {"norm", "mixer", "ffn", "updates"}
+        if unknown or spec.part("norm") is None or spec.part("mixer") is None:
+            raise ValueError("shared_norm_parallel takes the parts norm, mixer, ffn and updates"
+                             + (f"; got also {sorted(unknown)}" if unknown else ""))
+        self.norm: Norm = build_part("norm", spec.part("norm"), width=hidden_size)
+        self.mixer: Mixer = build_part("mixer", spec.part("mixer"), hidden_size=hidden_size)
+        self.ffn: Optional[FeedForward] = None
+        if spec.part("ffn") is not None:
+            self.ffn = build_part("feed_forward", spec.part("ffn"), hidden_size=hidden_size)
+        self.updates = [build_part("stream_update", u, hidden_size=hidden_size) for u in (spec.part("updates") or ())]
+
+    def parts(self) -> List[Part]:
+        return [self.norm, self.mixer] + ([self.ffn] if self.ffn is not None else []) + list(self.updates)
+
+    def branch_buffers_needed(self) -> int:
+        return 2
+
+    def state_specs(self) -> List[Tuple[str, StateSpec]]:
+        return [(f"{self.mixer.name}.{s.name}", s) for s in self.mixer.state_specs()]
+
+    def finalize(self, dtype: torch.dtype, device: torch.device) -> None:
+        for p in self.parts():
+            p.finalize(dtype, device)
+
+    def streamed_weights(self) -> List[Tensor]:
+        ws = [self.mixer.input_weight() if self.mixer.input_rows() > 0 else None, self.mixer.output_weight()]
+        if self.ffn is not None:
+            ws += list(self.ffn.streamed_weights())
+        return [w for w in ws if w is not None]
+
+    def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
+        ws = ctx.workspace
+        mark = ws.mark()
+        n = stream.normed(self.norm)
+        mixed = stream.take_branch()
+        if self.ffn is None:
+            self.mixer.forward(n, ctx, cache, mixed)
+            stream.add(mixed, self.mixer.out_scale)
+        else:
+            fed = stream.take_branch()
+            if n.is_cuda and _PARALLEL_MIXERS:
+                main = torch.cuda.current_stream(n.device)
+                side = branches.branch_stream(n.device, "mixer")
+                with branches.fork(main, side):
+                    self.mixer.forward(n, ctx, cache, mixed)
+                self.ffn.forward(n, ctx, fed)
+                main.wait_stream(side)
+            else:
+                self.mixer.forward(n, ctx, cache, mixed)
+                self.ffn.forward(n, ctx, fed)
+            stream.add(mixed, self.mixer.out_scale)
+            stream.add(fed, self.ffn.out_scale)
+        for update in self.updates:
+            update.forward(stream, ctx)
+        ws.release(mark)
+
+
+def shared_norm_layer(prefix: str, norm: PartSpec, mixer: PartSpec, ffn: Optional[PartSpec] = None, updates=()) -> LayerSpec:
+    """The LayerSpec of a ``shared_norm_parallel`` layer."""
+    return LayerSpec("shared_norm_parallel", prefix, {"norm": norm, "mixer": mixer, "ffn": ffn, "updates": tuple(updates)})
+
+
 register_arrangement("parallel_prenorm", ParallelPreNormBlock)
+register_arrangement("shared_norm_parallel", SharedNormParallelBlock)

@@ -147,4 +147,118 @@ class RoutedGLU(FeedForward):
         return [w for w in (self.shared_gate_up, self.shared_down) if w is not None]
 
 
+class RoutedScored(FeedForward):
+    """A mixture of small ungated experts chosen by sigmoid scores, optionally beside a gated shared one.
+
+        z = Wr x (float arithmetic), s = sigmoid(z); the choice runs on s + correction (``correction``: a stored
+        vector [E]), and only among the experts of the ``keep`` groups (of ``groups`` equal groups of neighbouring
+        experts) whose two largest s + correction sum highest; the ``top`` largest are chosen;
+        their weights are their s divided by the sum of the chosen s (+ 1e-20), times ``scale``;
+        expert e:  y_e = Wd_e max(Wu_e x, 0)^2;   out = sum over the chosen e of weight_e y_e
+        (+ sigmoid(w_sg . x) * the shared expert's output, same form with its own width, for every token).
+
+    Tensors: ``router`` [E, D], ``correction`` [E], ``e<i>.up`` [F, D], ``e<i>.down`` [D, F], ``shared.up`` [Fs, D],
+    ``shared.down`` [D, Fs], ``shared.sg`` [1, D].  The chain of launches is RoutedGLU's: route (with the shared
+    expert's gate as one more row), plan, the grouped up product with the activation in its epilogue, the grouped
+    down product, and the weighted sum, which adds the gated shared expert."""
+
+    def __init__(self, hidden_size: int, experts: int, top: int, expert_ff: int, scale: float = 1.0, groups: int = 1,
+                 keep: int = 1, correction: bool = True, shared_ff: int = 0, shared_gate: bool = True,
+                 out_multiplier: float = 1.0):
+        if not 1 <= top <= experts:
+            raise ValueError("top must be between 1 and the number of experts")
+        if expert_ff <= 0 or shared_ff < 0:
+            raise ValueError("expert widths must be positive")
+        if groups < 1 or experts % groups or not 1 <= keep <= groups or top > keep * (experts // groups):
+            raise ValueError("groups must divide the experts, keep <= groups, top <= keep * experts / groups")
+        self.hidden_size = int(hidden_size)
+        self.experts, self.top, self.expert_ff = int(experts), int(top), int(expert_ff)
+        self.scale, self.groups, self.keep = float(scale), int(groups), int(keep)
+        self.has_correction, self.shared_ff = bool(correction), int(shared_ff)
+        self.has_shared_gate = bool(shared_gate) and self.shared_ff > 0
+        self.out_scale = float(out_multiplier)
+
+    def param_specs(self) -> List[ParamSpec]:
+        D, F = self.hidden_size, self.expert_ff
+        specs = [ParamSpec("router", (self.experts, D), kind="vector", init=("normal", 0.5))]
+        if self.has_correction:
+            specs.append(ParamSpec("correction", (self.experts,), kind="vector", init=("normal", 0.2)))
+        for e in range(self.experts):
+            specs += [ParamSpec(f"e{e}.up", (F, D), init=("normal", 0.1)), ParamSpec(f"e{e}.down", (D, F), init=("normal", 0.1))]
+        if self.shared_ff > 0:
+            Fs = self.shared_ff
+            specs += [ParamSpec("shared.up", (Fs, D), init=("normal", 0.1)), ParamSpec("shared.down", (D, Fs), init=("normal", 0.1))]
+            if self.has_shared_gate:
+                specs.append(ParamSpec("shared.sg", (1, D), kind="vector", init=("normal", 0.5)))
+        return specs
+
+    def bind(self, params: Dict[str, Tensor]) -> None:
+        E = self.experts
+        self.router_w = params["router"].contiguous()
+        self.correction = params["correction"].contiguous() if self.has_correction else None
+        self.up = torch.stack([params[f"e{e}.up"] for e in range(E)]).contiguous()
+        self.down = torch.stack([params[f"e{e}.down"] for e in range(E)]).contiguous()
+        self.shared_up: Optional[Tensor] = None
+        self.shared_down: Optional[Tensor] = None
+        self.shared_gate_w: Optional[Tensor] = None
+        if self.shared_ff > 0:
+            self.shared_up = params["shared.up"].contiguous()
+            self.shared_down = params["shared.down"].contiguous()
+            if self.has_shared_gate:
+                self.shared_gate_w = params["shared.sg"].reshape(-1).contiguous()
+
+    def _shared(self, x: Tensor, y: Tensor, ctx) -> None:
+        ws = ctx.workspace
+        act = ws.alloc((x.shape[0], self.shared_ff), x.dtype)
+        streaming.linear(x, self.shared_up, act, ctx)
+        K.relu_squared(act, act)
+        streaming.linear(act, self.shared_down, y, ctx)
+
+    def forward(self, x: Tensor, ctx, out: Tensor) -> None:
+        ws = ctx.workspace
+        T, D = x.shape
+        E, top, F = self.experts, self.top, self.expert_ff
+        A = T * top
+        ids = ws.alloc((T, top), torch.int32)
+        weights = ws.alloc((T, top), torch.float32)
+        gate = ws.alloc((T,), torch.float32) if self.shared_gate_w is not None else None
+        K.moe_route(x, self.router_w, None, top, ids, weights, scored=True, correction=self.correction,
+                    groups=self.groups, keep=self.keep, scale=self.scale, gate_w=self.shared_gate_w, gate_out=gate)
+        offsets = ws.alloc((E + 1,), torch.int32)
+        tile_start = ws.alloc((E + 1,), torch.int32)
+        perm = ws.alloc((A,), torch.int32)
+        act = ws.alloc((A, F), x.dtype)
+        y = ws.alloc((A, D), x.dtype)
+        shared = side = None
+        if self.shared_ff > 0:
+            shared = ws.alloc((T, D), x.dtype)
+            if x.is_cuda and _SIDE_SHARED:
+                main = torch.cuda.current_stream(x.device)
+                side = branches.branch_stream(x.device, "shared_expert")
+                with branches.fork(main, side):
+                    self._shared(x, shared, ctx)
+            else:
+                self._shared(x, shared, ctx)
+        if (_TC_MOE and A >= _TC_FROM_PAIRS and K.moe_tc_supported(x, self.up, F) and K.moe_tc_supported(act, self.down, D)):
+            K.moe_plan(ids, E, "tcgen05", offsets, tile_start, perm)
+            xs = ws.alloc((A, D), x.dtype)
+            K.moe_gather_rows(x, perm, top, xs)
+            K.moe_tc_gemm(xs, self.up, perm, offsets, tile_start, True, act, ungated=True)
+            K.moe_tc_gemm(act, self.down, perm, offsets, tile_start, False, y)
+        else:
+            form = "float"
+            if K.moe_gemm_tc_ok(x, self.up) and K.moe_gemm_tc_ok(act, self.down):
+                form = "mma_few" if A <= _FEW_PAIRS else "mma"
+            K.moe_plan(ids, E, form, offsets, tile_start, perm)
+            K.moe_gemm(x, self.up, perm, offsets, tile_start, top, True, act, form, ungated=True)
+            K.moe_gemm(act, self.down, perm, offsets, tile_start, top, False, y, form)
+        if side is not None:
+            main.wait_stream(side)
+        K.moe_combine(y, weights, shared, out, shared_gate=gate)
+
+    def streamed_weights(self) -> List[Tensor]:
+        return [w for w in (self.shared_up, self.shared_down) if w is not None]
+
+
 register_feed_forward("routed_glu", RoutedGLU)
+register_feed_forward("routed_scored", RoutedScored)
