@@ -23,7 +23,8 @@ L2 flush is needed between timed iterations.
 `--workload compare` is a measurement beside the benchmark (its own JSON line): a Boketar model (or, with
 `--design tafesun`, a Tafesun model) and a Falcon-H1 model of equal width, feed-forward size, layer count and
 vocabulary, one prompt step and decode steps of each with the L2 flushed before every timed step, and every
-kernel's device time.
+kernel's device time.  `--design gikovik` measures a Gikovik model beside the Tafesun model (the closest one:
+paged softmax attention and routed experts) in the same way.
 """
 from __future__ import annotations
 
@@ -521,6 +522,31 @@ def tafesun_config(falcon, ff_sizes, layers):
             "norm": {"eps": 1e-6}, "logit_scale": 1.0, "layers": out}
 
 
+# `--workload compare --design gikovik`: a Gikovik model beside the Tafesun model above (equal width, layer
+# runs, vocabulary, experts, experts a token and expert widths).  Layers with a sink and layers with a rotated
+# part take turns; the cache row of both is 128 entries (a latent of 128, or of 96 beside 32 rotated ones); with
+# at least four layers the model is a loop that runs twice, as the Tafesun model's second half borrows the
+# tensors of its first.  name -> (heads, unrotated key entries and value entries per head, query latent).
+GIKOVIK_MIXER = {"0.5b": (8, 64, 64, 384), "7b": (24, 128, 128, 1536)}
+
+
+def gikovik_config(falcon, mixer_sizes, ff_sizes, layers):
+    experts, top, expert_ff, shared_ff = ff_sizes
+    heads, dim, vdim, q_rank = mixer_sizes
+    scale = (dim + 32) ** -0.5
+    sink = {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": 128, "scale": dim ** -0.5}
+    rotated = {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": 96, "scale": scale, "rot_dim": 32,
+               "rot": {"dims": 32, "base": 1e4}}
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}}
+    own = layers // 2 if layers >= 4 and layers % 2 == 0 else layers
+    out = [{"type": "latent_attention_2" if i % 2 else "latent_attention", "mixer": rotated if i % 2 else sink, "mlp": mlp}
+           for i in range(own)]
+    return {"architecture": "Gikovik", "vocab": falcon["vocab_size"], "width": falcon["hidden_size"], "norm": {"eps": 1e-6},
+            "loop": {"start": 0, "stop": own, "times": 2} if own < layers else None, "token_side": {"dim": 32},
+            "layers": out}
+
+
 def compare_workload(args, peaks) -> int:
     import torch
 
@@ -535,7 +561,12 @@ def compare_workload(args, peaks) -> int:
     falcon.update(falcon_keys)
     falcon["num_hidden_layers"] = layers
     vocab = falcon["vocab_size"]
-    if args.design == "tafesun":
+    if args.design == "gikovik":
+        configs = {"gikovik": gikovik_config(falcon, GIKOVIK_MIXER[args.sizes], TAFESUN_FF[args.sizes], layers),
+                   "tafesun": tafesun_config(falcon, TAFESUN_FF[args.sizes], layers)}
+        design_sizes = {"routed_ff": dict(zip(("experts", "top", "expert_ff", "shared_ff"), TAFESUN_FF[args.sizes])),
+                        "gikovik_mixer": dict(zip(("heads", "dim", "vdim", "q_rank"), GIKOVIK_MIXER[args.sizes]))}
+    elif args.design == "tafesun":
         configs = {"tafesun": tafesun_config(falcon, TAFESUN_FF[args.sizes], layers), "falcon_h1": falcon}
         design_sizes = {"tafesun_ff": dict(zip(("experts", "top", "expert_ff", "shared_ff"), TAFESUN_FF[args.sizes]))}
     else:
@@ -659,8 +690,8 @@ def main() -> int:
                          "count (--layers, default 4) and vocabulary at --sizes 0.5b or 7b: one prompt step of "
                          "--prompt-tokens and decode steps of --batch requests at --context, device-timed with the "
                          "L2 flushed, and the device time of every kernel of one step of each")
-    ap.add_argument("--design", default="boketar", choices=["boketar", "tafesun"],
-                    help="--workload compare: the model that is measured beside Falcon-H1")
+    ap.add_argument("--design", default="boketar", choices=["boketar", "tafesun", "gikovik"],
+                    help="--workload compare: the model that is measured beside Falcon-H1 (gikovik: beside Tafesun)")
     ap.add_argument("--no-check", dest="check", action="store_false",
                     help="skip the comparison with the plain implementation that runs before the timing: the first "
                          "two layers of the run's model, in the run's dtype, on the benchmark's schedule (a "

@@ -1540,19 +1540,21 @@ def token_gated_update_fits(width: int, rank: int) -> bool:
 
 
 def token_gated_update(h: Tensor, branches: Sequence[Tuple[Tensor, float]], tokens: Tensor, table: Tensor, col0: int,
-                       w_gate: Tensor, w_proj: Tensor, norm_w: Tensor, eps: float) -> None:
+                       w_gate: Tensor, w_proj_t: Tensor, norm_w: Tensor, eps: float) -> None:
     """h <- x + rms(Wp (gelu_tanh(Wg x) * e)) * norm_w with x = h + sum(scale_i * branch_i) (at most two branches)
-    and e = table[token, col0 : col0 + R]; h [T, D] float32 in place, Wg [R, D], Wp [D, R]."""
+    and e = table[token, col0 : col0 + R]; h [T, D] float32 in place, Wg [R, D], Wp given transposed: Wp^T [R, D]
+    (its rows are then read side by side)."""
     items = list(branches)
+    w_proj = w_proj_t
     _cuda(h, tokens, table, w_gate, w_proj, norm_w, *[b for b, _ in items])
     T, D = h.shape
     R = w_gate.shape[0]
     if not (h.dtype == torch.float32 and h.is_contiguous() and len(items) <= 2):
         raise KernelError("token_gated_update: h contiguous float32 and at most two branches")
-    if not (w_gate.shape == (R, D) and w_proj.shape == (D, R) and w_gate.is_contiguous() and w_proj.is_contiguous()
+    if not (w_gate.shape == (R, D) and w_proj.shape == (R, D) and w_gate.is_contiguous() and w_proj.is_contiguous()
             and w_gate.dtype == w_proj.dtype == table.dtype and table.dim() == 2 and table.stride(1) == 1
             and 0 <= col0 and col0 + R <= table.shape[1]):
-        raise KernelError("token_gated_update: Wg [R, D], Wp [D, R] and the table of one type, the columns inside it")
+        raise KernelError("token_gated_update: Wg [R, D], Wp^T [R, D] and the table of one type, the columns inside it")
     for b, _ in items:
         if not (b.shape == h.shape and b.is_contiguous() and b.dtype == w_gate.dtype):
             raise KernelError("token_gated_update: branches contiguous [T, D] of the matrices' type")

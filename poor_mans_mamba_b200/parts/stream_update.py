@@ -51,12 +51,12 @@ class TokenGatedUpdate(StreamUpdate):
     def bind(self, params: Dict[str, Tensor]) -> None:
         g, p, n = self.tensors
         self.table = params[self.table_name]
-        self.w_gate, self.w_proj = params[g].contiguous(), params[p].contiguous()
+        self.w_gate, self.w_proj_t = params[g].contiguous(), params[p].t().contiguous()  # Wp^T [R, D]
         self.norm_w = params[n].contiguous()
 
     def forward(self, stream, ctx) -> None:
         K.token_gated_update(stream.h, stream.take_pending(2), ctx.tokens, self.table, self.column, self.w_gate,
-                             self.w_proj, self.norm_w, self.eps)
+                             self.w_proj_t, self.norm_w, self.eps)
 
 
 class EmbeddingReentry(StreamUpdate):

@@ -1,0 +1,312 @@
+"""Gikovik through the engine against the plain implementation (GPU): every way of cutting the
+work, tiny configurations that differ in every size and option, float32 and bfloat16."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import gpu_harness as H
+import gikovik_configs as C
+from plain import gikovik_plain as P
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+F32_FRAC = 2e-5
+LENGTHS = (1, 2, 9, 40, 77, 131, 203)
+
+
+def check_rows(got, ref, dtype, what, f32_frac=F32_FRAC):
+    """float32: every logit within ``f32_frac`` of the largest one.  bfloat16: the token input divides a vector
+    that comes out of a bottleneck of three to six entries by its root mean square, so at a position where that
+    vector is nearly zero the rounding of the layer's branches is magnified many times; such positions are few.
+    Every row must be within three times the usual bound and all but one in fifty within the bound itself."""
+    if dtype == "float32":
+        return H.check_rows(got, ref, dtype, what, f32_frac=f32_frac)
+    got = got.detach().double().cpu()
+    assert got.shape == ref.shape and bool(torch.isfinite(got).all()), what
+    frac = (got - ref).abs().max(dim=1).values / float(ref.abs().max())
+    over = int((frac > H.BF16_FRAC).sum())
+    assert float(frac.max()) <= 3 * H.BF16_FRAC, f"{what}: row {int(frac.argmax())} is off by {float(frac.max()):.3f} of the largest logit"
+    assert over <= max(1, len(frac) // 50), f"{what}: {over} of {len(frac)} rows over {H.BF16_FRAC}, first {int((frac > H.BF16_FRAC).nonzero()[0])}"
+
+
+def refs_of(cfg, weights, seqs):
+    return [P.forward(cfg, weights, s, torch.float64) for s in seqs]
+
+
+class Case:
+    """A configuration with two sets of weights: freely routed tokens for float32, decisive routers for bfloat16
+    (see gikovik_configs.decisive_routers)."""
+
+    def __init__(self, which, tmp, lengths=LENGTHS, seq_seed=7, seed=None, edit=None, patch=None):
+        self.which = which if isinstance(which, str) else "custom"
+        seed = ord(self.which[0]) if seed is None else seed
+        self.by_dtype = {}
+        for dtype, routers in (("float32", None), ("bfloat16", C.decisive_routers)):
+            def both(w, routers=routers):
+                if edit:
+                    edit(w)
+                if routers:
+                    routers(w)
+            d, cfg, weights = C.make_model_dir(which, str(tmp / dtype), seed=seed, edit=both, patch=patch)
+            self.cfg = cfg
+            self.seqs = C.sequences(cfg, lengths, seed=seq_seed)
+            self.by_dtype[dtype] = (d, weights, refs_of(cfg, weights, self.seqs))
+
+    def of(self, dtype):
+        return self.by_dtype[dtype]
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def case(request, tmp_path_factory):
+    return Case(request.param, tmp_path_factory.mktemp(f"gk{request.param}"))
+
+
+def test_the_stream_after_every_layer_run(case):
+    """The float32 residual stream after every run of a layer (a looped layer counts each time) against the
+    plain implementation: the first difference names the layer and the run."""
+    d, weights, refs = case.of("float32")
+    seq = case.seqs[3]
+    want = []
+    P.forward(case.cfg, weights, seq, torch.float64, collect=want)
+    runner = H.make_runner(d, "float32", page_size=16, num_pages=8, num_slots=1)
+    got = []
+    for layer in runner.model.layers:
+        def forward(stream, ctx, cache, orig=layer.forward):
+            orig(stream, ctx, cache)
+            got.append(stream.flush().clone())
+        layer.forward = forward
+    H.run_script(runner, [seq], H.script_whole([seq]))
+    assert len(got) == len(want) == len(P.layer_runs(case.cfg))
+    for run, (g, w) in enumerate(zip(got, want)):
+        err = float((g.double().cpu() - w).abs().max())
+        assert err <= 2e-5 * max(1.0, float(w.abs().max())), f"{case.which}: stream after run {run}: {err:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
+def test_cuttings_agree_with_plain(case, dtype, cutting):
+    which, seqs = case.which, case.seqs
+    d, weights, refs = case.of(dtype)
+    page_size = 16
+    if cutting == "mixed":
+        # so few pages and slots that they are used again
+        budget = max((len(s) + page_size - 1) // page_size for s in seqs) + 5
+        runner = H.make_runner(d, dtype, page_size=page_size, num_pages=budget, num_slots=3)
+        script = H.script_mixed(seqs, max_live=3, seed=5, budget_pages=budget, page_size=page_size)
+        assert any(len(p) > 1 and any(n == 1 for _, _, n in p) and any(n > 1 for _, _, n in p) for p, _ in script)
+    else:
+        runner = H.make_runner(d, dtype, page_size=page_size, num_pages=16, num_slots=2)
+        script = {"whole": H.script_whole, "portions": H.script_portions,
+                  "tail": lambda s: H.script_tail_one_by_one(s, tail=70)}[cutting](seqs)
+    out = H.run_script(runner, seqs, script)
+    for i, ref in enumerate(refs):
+        check_rows(out[i], ref, dtype, f"{which} {dtype} {cutting} seq {i} (len {len(seqs[i])})", f32_frac=F32_FRAC)
+    for g in runner.cache.groups.values():
+        assert g.pool.n_free == g.num_pages  # every page came back
+    assert runner.cache.free_slots == runner.cache.num_slots
+
+
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_portions_of_two_tokens_and_page_borders(case, page_size):
+    """Every portion is two tokens long (then three, so that both parities of a page's edge are met),
+    against the whole prompt."""
+    which, seqs = case.which, case.seqs
+    d, weights, refs = case.of("float32")
+    i = 5
+    for width in (2, 3):
+        runner = H.make_runner(d, "float32", page_size=page_size, num_pages=max(4, 256 // page_size), num_slots=1)
+        n = len(seqs[i])
+        script = [([(i, a, min(width, n - a))], [i] if a + width >= n else []) for a in range(0, n, width)]
+        out = H.run_script(runner, seqs, script)
+        check_rows(out[i], refs[i], "float32", f"{which} portions of {width}", f32_frac=F32_FRAC)
+
+
+def test_long_decoding_from_the_first_token(case):
+    """One prompt token, then 202 tokens one by one: the latents of decoded tokens fill page after page, in
+    every pass of the loop on pages of its own."""
+    which, seqs = case.which, case.seqs
+    for dtype in ("float32", "bfloat16"):
+        d, weights, refs = case.of(dtype)
+        runner = H.make_runner(d, dtype, page_size=16, num_pages=16, num_slots=1)
+        out = H.run_script(runner, seqs[6:7], H.script_tail_one_by_one(seqs[6:7], tail=len(seqs[6]) - 1))
+        check_rows(out[0], refs[6], dtype, f"{which} {dtype} long decoding", f32_frac=F32_FRAC)
+
+
+def test_batch_of_unequal_requests_equals_each_alone(case):
+    which, seqs = case.which, case.seqs
+    for dtype in ("float32", "bfloat16"):
+        d, weights, refs = case.of(dtype)
+        runner = H.make_runner(d, dtype, page_size=16, num_pages=40, num_slots=4)
+        pick = [1, 3, 4, 6]
+        half = {i: len(seqs[i]) // 2 for i in pick}
+        script = [([(i, 0, half[i]) for i in pick], []),
+                  ([(i, half[i], len(seqs[i]) - half[i]) for i in pick], pick)]
+        out = H.run_script(runner, seqs, script)
+        for i in pick:
+            check_rows(out[i], refs[i], dtype, f"{which} {dtype} batched seq {i}", f32_frac=F32_FRAC)
+
+
+def test_slot_and_pages_used_again_start_clean(case):
+    """A request that takes the slot and pages of a finished one sees nothing of it."""
+    which, seqs = case.which, case.seqs
+    d, weights, refs = case.of("float32")
+    runner = H.make_runner(d, "float32", page_size=16, num_pages=13, num_slots=1)
+    script = [([(6, 0, 203)], [6]), ([(5, 0, 50)], []), ([(5, 50, 81)], [5]), ([(3, 0, 40)], [3])]
+    out = H.run_script(runner, seqs, script)
+    for i in (6, 5, 3):
+        check_rows(out[i], refs[i], "float32", f"{which} reuse seq {i}", f32_frac=F32_FRAC)
+
+
+def _loud(weights, cfg):
+    """Weights under which a lost key, a sink left out or a wrong angle cannot hide.  In both kinds of mixer
+    the first head's query and key are made large along one unrotated entry, so that single scores stand out
+    by far wherever their keys lie (hundreds of tokens back, across pages); the rotated parts are made large
+    as a whole, so that the positions decide scores; and the sinks are raised to the level of those scores,
+    so that they take a visible share of the weight."""
+    for i, layer in enumerate(cfg["layers"][:2]):   # one layer of either kind
+        m, p = layer["mixer"], f"l{i}.mix."
+        d, rd = m["dim"], m.get("rot_dim", 0)
+        weights[p + "uq"][d - 1] *= 4.0
+        weights[p + "uk"][d - 1] *= 4.0
+        if rd:
+            weights[p + "uq"][d:d + rd] *= 3.0
+            weights[p + "dkv"][m["kv_rank"]:] *= 3.0
+        else:
+            weights[p + "sink"] += 4.0
+
+
+def test_loud_far_keys_sinks_and_positions(tmp_path):
+    case = Case("A", tmp_path, lengths=(300,), seq_seed=3, seed=11, edit=lambda w: _loud(w, C.GK_A))
+    seqs, cfg = case.seqs, case.cfg
+    for dtype in ("float32", "bfloat16"):
+        d, weights, refs = case.of(dtype)
+        ref = refs[0]
+        # the oracle itself: with the far tokens changed, without the sinks, or with positions that start at
+        # one, the last logits move visibly
+        other = list(seqs[0])
+        other[:40] = C.sequences(cfg, (40,), seed=99)[0]
+        assert float((P.forward(cfg, weights, other, torch.float64)[-20:] - ref[-20:]).abs().max()) > 0.05
+        no_sink = {k: (v - 50.0 if k.endswith("mix.sink") else v) for k, v in weights.items()}
+        assert float((P.forward(cfg, no_sink, seqs[0], torch.float64) - ref).abs().max()) > 0.05
+        for script in (H.script_whole(seqs), H.script_tail_one_by_one(seqs, tail=64), H.script_portions(seqs, seed=2)):
+            runner = H.make_runner(d, dtype, page_size=16, num_pages=24, num_slots=1)
+            out = H.run_script(runner, seqs, script)
+            check_rows(out[0], ref, dtype, f"loud {dtype}", f32_frac=4e-5)
+
+
+def test_options_that_one_model_leaves_equal(tmp_path):
+    """Configuration B without groups in its first router and with a loop over its last two layers that runs
+    once: a loop of one pass still replaces the stream by the product of itself and the embedding's output."""
+    def patch(cfg):
+        cfg["loop"] = {"start": 1, "stop": 3, "times": 1}
+        del cfg["layers"][0]["mlp"]["router"]["groups"]
+        cfg["layers"][1]["mlp"]["router"]["groups"] = {"count": 9, "keep": 4}   # groups of a single expert
+        cfg["layers"][1]["mlp"]["router"]["top"] = 3
+    case = Case(C.GK_B, tmp_path, lengths=(57, 18), patch=patch, seed=31)
+    seqs = case.seqs
+    for dtype in ("float32", "bfloat16"):
+        d, weights, refs = case.of(dtype)
+        for script in (H.script_whole(seqs), H.script_portions(seqs, seed=4)):
+            runner = H.make_runner(d, dtype, page_size=16, num_pages=8, num_slots=1)
+            out = H.run_script(runner, seqs, script)
+            for i, ref in enumerate(refs):
+                check_rows(out[i], ref, dtype, f"options {dtype} seq {i}", f32_frac=F32_FRAC)
+
+
+def test_greedy_generation_through_the_engine(case):
+    """Engine.generate (scheduler, sampler, decode graphs) against greedy decoding with the plain
+    implementation, float32; bfloat16 with graphs against bfloat16 step by step."""
+    from poor_mans_mamba_b200.entry import Engine
+    which, seqs, cfg = case.which, case.seqs, case.cfg
+    d, weights, refs = case.of("float32")
+    prompts = [seqs[2], seqs[3][:23], seqs[1]]
+    n_new = 12
+    eng = Engine(d, dtype="float32", max_tokens=1024, max_seqs=4, page_size=16, max_batched_tokens=32)
+    got = eng.generate(prompts, max_new_tokens=n_new, eos_token_id=-1)
+    for p, g in zip(prompts, got):
+        toks = list(p)
+        for _ in range(n_new):
+            lg = P.forward(cfg, weights, toks, torch.float64)[-1]
+            top2 = torch.topk(lg, 2).values
+            if float(top2[0] - top2[1]) < 1e-3:
+                break  # a near tie: the two may disagree from here on without either being wrong
+            toks.append(int(lg.argmax()))
+        want = toks[len(p):]
+        assert g[:len(want)] == want
+    d = case.of("bfloat16")[0]
+    a = Engine(d, dtype="bfloat16", max_tokens=1024, max_seqs=4, page_size=16, cuda_graphs=True).generate(
+        prompts, max_new_tokens=n_new, eos_token_id=-1)
+    b = Engine(d, dtype="bfloat16", max_tokens=1024, max_seqs=4, page_size=16, cuda_graphs=False).generate(
+        prompts, max_new_tokens=n_new, eos_token_id=-1)
+    assert a == b
+
+
+def test_trace_program_replays_a_schedule(case, tmp_path):
+    which, seqs, cfg = case.which, case.seqs, case.cfg
+    if which != "A":
+        pytest.skip("one configuration is enough for the program")
+    steps = [
+        {"step": 0, "entries": [{"id": "x", "tokens": seqs[3][:17], "want": [0, 16]},
+                                {"id": "y", "tokens": seqs[2], "want": [8]}], "end": ["y"]},
+        {"step": 1, "entries": [{"id": "x", "tokens": seqs[3][17:19], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "x", "tokens": seqs[3][19:], "want": [len(seqs[3]) - 20]},
+                                {"id": "z", "tokens": seqs[1], "want": [1]}], "end": ["x", "z"]},
+    ]
+    for dtype in ("float32", "bfloat16"):
+        d, weights, refs = case.of(dtype)
+        out_dir = str(tmp_path / f"out_{dtype}")
+        proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype,
+                               "--out", out_dir, "--max-tokens", "128"],
+                              input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                              timeout=600)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+        V = cfg["vocab"]
+        s0 = np.fromfile(os.path.join(out_dir, "0.f32"), dtype="<f4").reshape(-1, V)
+        s2 = np.fromfile(os.path.join(out_dir, "2.f32"), dtype="<f4").reshape(-1, V)
+        assert not os.path.exists(os.path.join(out_dir, "1.f32"))
+        want0 = torch.stack([refs[3][0], refs[3][16], refs[2][8]])
+        want2 = torch.stack([refs[3][-1], refs[1][1]])
+        check_rows(torch.from_numpy(s0), want0, dtype, "trace step 0", f32_frac=F32_FRAC)
+        check_rows(torch.from_numpy(s2), want2, dtype, "trace step 2", f32_frac=F32_FRAC)
+
+
+def test_command_line_generates_from_a_model_folder(case):
+    which, seqs, cfg = case.which, case.seqs, case.cfg
+    d, weights, refs = case.of("float32")
+    if which != "B":
+        pytest.skip("one configuration is enough for the program")
+    prompt = ",".join(str(t) for t in seqs[2])
+    proc = subprocess.run([sys.executable, "-m", "poor_mans_mamba_b200", d, "64", "GPU", "1", "2", "5", "--dtype", "float32",
+                           "--prompt-ids", prompt, "--page-size", "16"], capture_output=True, text=True, timeout=600,
+                          cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [l for l in proc.stdout.splitlines() if l.startswith("req_id=")]
+    assert len(lines) == 2 and all("gen_tokens=5" in l for l in lines)
+    toks = list(seqs[2])
+    for _ in range(5):
+        toks.append(int(P.forward(cfg, weights, toks, torch.float64)[-1].argmax()))
+    assert str(toks[len(seqs[2]):]) in lines[0]
+
+
+def test_medium_sizes_where_the_tensor_core_forms_run(tmp_path):
+    """Cache rows of 64 and 128 entries, prompts long enough for the tcgen05 attention, expert rows that the
+    tensor-core grouped products take, pages of 64 tokens: whole, in portions that cut pages anywhere, and
+    with a long tail decoded through the decode attention."""
+    case = Case("M", tmp_path, lengths=(700, 333), seq_seed=9, seed=21)
+    seqs = case.seqs
+    for dtype in ("float32", "bfloat16"):
+        d, weights, refs = case.of(dtype)
+        for name, script in (("whole", H.script_whole(seqs)),
+                             ("tail", H.script_tail_one_by_one(seqs, tail=80)),
+                             ("portions", [([(0, 0, 257)], []), ([(0, 257, 2), (1, 0, 130)], []),
+                                           ([(0, 259, 300), (1, 130, 1)], []), ([(0, 559, 141), (1, 131, 202)], [0, 1])])):
+            runner = H.make_runner(d, dtype, page_size=64, num_pages=20, num_slots=2)
+            out = H.run_script(runner, seqs, script)
+            for i, ref in enumerate(refs):
+                check_rows(out[i], ref, dtype, f"medium {dtype} {name} seq {i}", f32_frac=4e-5)
