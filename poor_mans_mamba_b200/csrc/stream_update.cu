@@ -14,6 +14,7 @@
 //
 // relu_squared: out = max(x, 0)^2, element-wise.
 #include "common.cuh"
+#include "mma_helpers.cuh"
 
 namespace pmm {
 
@@ -41,19 +42,26 @@ __global__ void __launch_bounds__(kSideThreads)
                               const int* __restrict__ tokens, const S* __restrict__ table, long long ld_table, int col0,
                               const S* __restrict__ w_gate, const S* __restrict__ w_proj_t, const float* __restrict__ norm_w,
                               float eps, int T, int D, int R) {
-  extern __shared__ __align__(16) float side_smem[];  // x [TOK][D] | y [TOK][D] | g [TOK][R]
-  __shared__ float red[32];
+  extern __shared__ __align__(16) float side_smem[];  // x [TOK][D] | y [TOK][D] | g [TOK][R] | e [TOK][R]
+  __shared__ float red[TOK * (kSideThreads / 32)];
   float* xs = side_smem;
   float* ys = xs + static_cast<size_t>(TOK) * D;
   float* gs = ys + static_cast<size_t>(TOK) * D;
+  float* es = gs + TOK * R;
   pdl_launch_dependents();
   pdl_wait();
   const int t0 = blockIdx.x * TOK;
   const int nt = min(TOK, T - t0);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // the tokens' table entries, fetched beside the rows of the stream (two dependent reads a token, all in flight at once)
+  for (int idx = threadIdx.x; idx < TOK * R; idx += kSideThreads) {
+    const int r = idx / R, j = idx - r * R;
+    es[idx] = r < nt ? ldf(table + static_cast<long long>(tokens[t0 + r]) * ld_table + col0 + j) : 0.f;
+  }
   // x = h + sa * a + sb * b; the rows of a short last block that have no token are zero
   if (VEC) {
     const int per_row = D >> 2;
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < TOK * per_row; idx += kSideThreads) {
       const int r = idx / per_row, i = (idx - r * per_row) << 2;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -86,36 +94,51 @@ __global__ void __launch_bounds__(kSideThreads)
     }
   }
   __syncthreads();
-  // g[r][j] = gelu(Wg[j] . x_r) * e_r[j]: a warp per row of Wg, read once for the block's tokens
-  for (int j = warp; j < R; j += kSideThreads / 32) {
-    const S* wr = w_gate + static_cast<size_t>(j) * D;
-    float acc[TOK];
+  // g[r][j] = gelu(Wg[j] . x_r) * e_r[j]: the rows of Wg are read once for the block's tokens; a warp takes four
+  // rows at a time (VEC), so that their reads are in flight together and a piece of x serves four rows
+  if (VEC) {
+    for (int j0 = warp << 2; j0 < R; j0 += (kSideThreads / 32) << 2) {
+      float acc[4][TOK];
 #pragma unroll
-    for (int r = 0; r < TOK; ++r) acc[r] = 0.f;
-    if (VEC) {
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int r = 0; r < TOK; ++r) acc[q][r] = 0.f;
+      const S* wr = w_gate + static_cast<size_t>(j0) * D;
+#pragma unroll 2
       for (int i = lane << 2; i < D; i += 128) {
-        const float4 w = ld4(wr + i);
+        float4 w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) w[q] = ld4(wr + static_cast<size_t>(q) * D + i);
 #pragma unroll
         for (int r = 0; r < TOK; ++r) {
           const float4 x = *reinterpret_cast<const float4*>(xs + r * D + i);
-          acc[r] += w.x * x.x + w.y * x.y + w.z * x.z + w.w * x.w;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) acc[q][r] += w[q].x * x.x + w[q].y * x.y + w[q].z * x.z + w[q].w * x.w;
         }
       }
-    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int r = 0; r < TOK; ++r) {
+          const float sum = warp_sum(acc[q][r]);
+          if (lane == 0) gs[r * R + j0 + q] = gelu_tanh_f(sum) * es[r * R + j0 + q];
+        }
+    }
+  } else {
+    for (int j = warp; j < R; j += kSideThreads / 32) {
+      const S* wr = w_gate + static_cast<size_t>(j) * D;
+      float acc[TOK];
+#pragma unroll
+      for (int r = 0; r < TOK; ++r) acc[r] = 0.f;
       for (int i = lane; i < D; i += 32) {
         const float wv = ldf(wr + i);
 #pragma unroll
         for (int r = 0; r < TOK; ++r) acc[r] += wv * xs[r * D + i];
       }
-    }
 #pragma unroll
-    for (int r = 0; r < TOK; ++r) {
-      const float sum = warp_sum(acc[r]);
-      if (lane == 0) {
-        float g = 0.f;
-        if (r < nt)
-          g = gelu_tanh_f(sum) * ldf(table + static_cast<long long>(tokens[t0 + r]) * ld_table + col0 + j);
-        gs[r * R + j] = g;
+      for (int r = 0; r < TOK; ++r) {
+        const float sum = warp_sum(acc[r]);
+        if (lane == 0) gs[r * R + j] = gelu_tanh_f(sum) * es[r * R + j];
       }
     }
   }
@@ -129,6 +152,7 @@ __global__ void __launch_bounds__(kSideThreads)
       float4 acc[TOK];
 #pragma unroll
       for (int r = 0; r < TOK; ++r) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
       for (int j = 0; j < R; j += 4) {
         float4 w[4];
 #pragma unroll
@@ -167,8 +191,18 @@ __global__ void __launch_bounds__(kSideThreads)
   }
   float inv[TOK];
 #pragma unroll
-  for (int r = 0; r < TOK; ++r)  // (block_sum syncs the block)
-    inv[r] = 1.f / sqrtf(block_sum(sq[r], red) / static_cast<float>(D) + eps);
+  for (int r = 0; r < TOK; ++r) {
+    sq[r] = warp_sum(sq[r]);
+    if (lane == 0) red[r * (kSideThreads / 32) + warp] = sq[r];
+  }
+  __syncthreads();  // (also: every thread's part of ys is written)
+#pragma unroll
+  for (int r = 0; r < TOK; ++r) {
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < kSideThreads / 32; ++k) total += red[r * (kSideThreads / 32) + k];
+    inv[r] = 1.f / sqrtf(total / static_cast<float>(D) + eps);
+  }
 #pragma unroll
   for (int r = 0; r < TOK; ++r) {
     if (r >= nt) continue;
@@ -183,6 +217,208 @@ __global__ void __launch_bounds__(kSideThreads)
       }
     } else {
       for (int i = threadIdx.x; i < D; i += kSideThreads) h[row + i] = xs[r * D + i] + ys[r * D + i] * inv[r] * norm_w[i];
+    }
+  }
+}
+
+// The same update on the tensor cores (bfloat16 storage, mma.sync m16n8k16 with float accumulation): a block
+// per 16 tokens, R = 16 * RK.  x enters the gate product rounded to bfloat16 and g the projection likewise; the
+// sums, the activation, the root mean square and the new stream are float, and x itself is read again from the
+// float stream and its branches for the final sum.  Wg x: the warps split D and their partial sums meet in
+// shared memory.  Wp g: the warps split the columns; the tiles are made twice (K is only R), first for the
+// sum of squares and then for the stream, so that no row of y waits anywhere, whatever D is.
+constexpr int kSideMmaThreads = 512, kSideMmaWarps = kSideMmaThreads / 32, kSideMmaTok = 16;
+constexpr int kSideMmaFromTokens = 1024;  // below, a block per token on the CUDA cores fills the SMs better
+
+inline size_t side_mma_smem_bytes(int D, int R) {
+  return static_cast<size_t>(kSideMmaTok) * (D + 8) * 2 + static_cast<size_t>(kSideMmaWarps) * kSideMmaTok * R * 4 +
+         static_cast<size_t>(kSideMmaTok) * R * 4 + static_cast<size_t>(kSideMmaWarps) * kSideMmaTok * 4 +
+         static_cast<size_t>(kSideMmaTok) * (R + 8) * 2;
+}
+
+template <int RK>
+__global__ void __launch_bounds__(kSideMmaThreads)
+    token_gated_update_mma_kernel(float* __restrict__ h, const bf16* __restrict__ a, float sa, const bf16* __restrict__ b,
+                                  float sb, const int* __restrict__ tokens, const bf16* __restrict__ table,
+                                  long long ld_table, int col0, const bf16* __restrict__ w_gate,
+                                  const bf16* __restrict__ w_proj, const float* __restrict__ norm_w, float eps, int T, int D) {
+  constexpr int R = 16 * RK, NT1 = 2 * RK, GS = R + 8;
+  extern __shared__ __align__(16) unsigned char side_mma_smem[];
+  const int XS = D + 8;                                             // row stride of xb: rows fall into different banks
+  bf16* xb = reinterpret_cast<bf16*>(side_mma_smem);                // [16][D + 8]
+  float* part = reinterpret_cast<float*>(xb + kSideMmaTok * XS);    // [warps][16][R]
+  float* es = part + kSideMmaWarps * kSideMmaTok * R;               // [16][R]
+  float* sqs = es + kSideMmaTok * R;                                // [warps][16]
+  bf16* gb = reinterpret_cast<bf16*>(sqs + kSideMmaWarps * kSideMmaTok);  // [16][R + 8]
+  pdl_launch_dependents();
+  const int t0 = blockIdx.x * kSideMmaTok;
+  const int nt = min(kSideMmaTok, T - t0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  // What does not depend on the launch before this one is asked for while that one still runs: the two matrices
+  // towards the L2 (every block a slice of their 128-byte lines, all blocks together all of them) and the
+  // tokens' table entries.
+  {
+    const int lines = (R * D * 2) >> 7;  // per matrix
+    const int mine = blockIdx.x * 16 + static_cast<int>(threadIdx.x);
+    if (threadIdx.x < 16 && lines > 0) {
+      const char* p0 = reinterpret_cast<const char*>(w_gate) + (static_cast<size_t>(mine % lines) << 7);
+      const char* p1 = reinterpret_cast<const char*>(w_proj) + (static_cast<size_t>(mine % lines) << 7);
+      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p0));
+      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p1));
+    }
+  }
+  for (int idx = threadIdx.x; idx < kSideMmaTok * R; idx += kSideMmaThreads) {
+    const int r = idx / R, j = idx - r * R;
+    es[idx] = r < nt ? ldf(table + static_cast<long long>(tokens[t0 + r]) * ld_table + col0 + j) : 0.f;
+  }
+  pdl_wait();
+  const int per_row = D >> 2;
+#pragma unroll 4
+  for (int idx = threadIdx.x; idx < kSideMmaTok * per_row; idx += kSideMmaThreads) {
+    const int r = idx / per_row, i = (idx - r * per_row) << 2;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < nt) {
+      const size_t at = static_cast<size_t>(t0 + r) * D + i;
+      v = ld4(h + at);
+      if (a) {
+        const float4 u = ld4(a + at);
+        v.x += sa * u.x, v.y += sa * u.y, v.z += sa * u.z, v.w += sa * u.w;
+      }
+      if (b) {
+        const float4 u = ld4(b + at);
+        v.x += sb * u.x, v.y += sb * u.y, v.z += sb * u.z, v.w += sb * u.w;
+      }
+    }
+    *reinterpret_cast<uint2*>(xb + r * XS + i) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+  }
+  __syncthreads();
+  {  // part[warp] = x[:, this warp's slices of D] Wg[:, the same]^T
+    float acc[NT1][4];
+#pragma unroll
+    for (int n = 0; n < NT1; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll 2
+    for (int k0 = warp * 16; k0 < D; k0 += kSideMmaWarps * 16) {
+      const bf16* xr = xb + g * XS + k0 + 2 * t;
+      unsigned af[4];
+      af[0] = *reinterpret_cast<const unsigned*>(xr);
+      af[1] = *reinterpret_cast<const unsigned*>(xr + 8 * XS);
+      af[2] = *reinterpret_cast<const unsigned*>(xr + 8);
+      af[3] = *reinterpret_cast<const unsigned*>(xr + 8 * XS + 8);
+      unsigned bf[NT1][2];
+#pragma unroll
+      for (int n = 0; n < NT1; ++n) {
+        const bf16* wr = w_gate + static_cast<size_t>(n * 8 + g) * D + k0 + 2 * t;
+        bf[n][0] = *reinterpret_cast<const unsigned*>(wr);
+        bf[n][1] = *reinterpret_cast<const unsigned*>(wr + 8);
+      }
+#pragma unroll
+      for (int n = 0; n < NT1; ++n) mma_bf16(acc[n], af, bf[n][0], bf[n][1]);
+    }
+    float* mine = part + warp * kSideMmaTok * R;
+#pragma unroll
+    for (int n = 0; n < NT1; ++n) {
+      *reinterpret_cast<float2*>(mine + g * R + n * 8 + 2 * t) = make_float2(acc[n][0], acc[n][1]);
+      *reinterpret_cast<float2*>(mine + (g + 8) * R + n * 8 + 2 * t) = make_float2(acc[n][2], acc[n][3]);
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < kSideMmaTok * R; idx += kSideMmaThreads) {
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kSideMmaWarps; ++w) sum += part[w * kSideMmaTok * R + idx];
+    const int r = idx / R, j = idx - r * R;
+    gb[r * GS + j] = __float2bfloat16_rn(gelu_tanh_f(sum) * es[idx]);
+  }
+  __syncthreads();
+  unsigned ga[RK][4];
+#pragma unroll
+  for (int kk = 0; kk < RK; ++kk) {
+    const bf16* gr = gb + g * GS + kk * 16 + 2 * t;
+    ga[kk][0] = *reinterpret_cast<const unsigned*>(gr);
+    ga[kk][1] = *reinterpret_cast<const unsigned*>(gr + 8 * GS);
+    ga[kk][2] = *reinterpret_cast<const unsigned*>(gr + 8);
+    ga[kk][3] = *reinterpret_cast<const unsigned*>(gr + 8 * GS + 8);
+  }
+  auto y_tile = [&](int tile, float* c) {
+    c[0] = c[1] = c[2] = c[3] = 0.f;
+    const bf16* wr = w_proj + static_cast<size_t>(tile * 8 + g) * R + 2 * t;
+    unsigned bf[RK][2];
+#pragma unroll
+    for (int kk = 0; kk < RK; ++kk) {
+      bf[kk][0] = *reinterpret_cast<const unsigned*>(wr + kk * 16);
+      bf[kk][1] = *reinterpret_cast<const unsigned*>(wr + kk * 16 + 8);
+    }
+#pragma unroll
+    for (int kk = 0; kk < RK; ++kk) mma_bf16(c, ga[kk], bf[kk][0], bf[kk][1]);
+  };
+  const int tiles = D >> 3;
+  float sq_lo = 0.f, sq_hi = 0.f;
+#pragma unroll 4
+  for (int tile = warp; tile < tiles; tile += kSideMmaWarps) {
+    float c[4];
+    y_tile(tile, c);
+    sq_lo += c[0] * c[0] + c[1] * c[1];
+    sq_hi += c[2] * c[2] + c[3] * c[3];
+  }
+  sq_lo += __shfl_xor_sync(0xffffffffu, sq_lo, 1);
+  sq_lo += __shfl_xor_sync(0xffffffffu, sq_lo, 2);
+  sq_hi += __shfl_xor_sync(0xffffffffu, sq_hi, 1);
+  sq_hi += __shfl_xor_sync(0xffffffffu, sq_hi, 2);
+  if (t == 0) {
+    sqs[warp * kSideMmaTok + g] = sq_lo;
+    sqs[warp * kSideMmaTok + g + 8] = sq_hi;
+  }
+  __syncthreads();
+  float tot_lo = 0.f, tot_hi = 0.f;
+#pragma unroll
+  for (int w = 0; w < kSideMmaWarps; ++w) {
+    tot_lo += sqs[w * kSideMmaTok + g];
+    tot_hi += sqs[w * kSideMmaTok + g + 8];
+  }
+  const float inv_lo = 1.f / sqrtf(tot_lo / static_cast<float>(D) + eps);
+  const float inv_hi = 1.f / sqrtf(tot_hi / static_cast<float>(D) + eps);
+  auto x_at = [&](int row, int col) {  // the stream with its branches at (row, col) and (row, col + 1)
+    float2 x = make_float2(0.f, 0.f);
+    if (row < nt) {
+      const size_t at = static_cast<size_t>(t0 + row) * D + col;
+      x = *reinterpret_cast<const float2*>(h + at);
+      if (a) {
+        const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(a + at));
+        x.x += sa * u.x, x.y += sa * u.y;
+      }
+      if (b) {
+        const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(b + at));
+        x.x += sb * u.x, x.y += sb * u.y;
+      }
+    }
+    return x;
+  };
+  // four tiles a turn: their reads of the stream are asked for together, before the first of their writes (the
+  // writes go to the array the reads come from, so the compiler keeps their order)
+  for (int tile0 = warp; tile0 < tiles; tile0 += 4 * kSideMmaWarps) {
+    float2 xv[4][2];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int tile = tile0 + u * kSideMmaWarps;
+      if (tile < tiles) {
+        xv[u][0] = x_at(g, tile * 8 + 2 * t);
+        xv[u][1] = x_at(g + 8, tile * 8 + 2 * t);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int tile = tile0 + u * kSideMmaWarps;
+      if (tile >= tiles) continue;
+      float c[4];
+      y_tile(tile, c);
+      const int col = tile * 8 + 2 * t;
+      const float2 w = *reinterpret_cast<const float2*>(norm_w + col);
+      if (g < nt)
+        *reinterpret_cast<float2*>(h + static_cast<size_t>(t0 + g) * D + col) =
+            make_float2(xv[u][0].x + c[0] * inv_lo * w.x, xv[u][0].y + c[1] * inv_lo * w.y);
+      if (g + 8 < nt)
+        *reinterpret_cast<float2*>(h + static_cast<size_t>(t0 + g + 8) * D + col) =
+            make_float2(xv[u][1].x + c[2] * inv_hi * w.x, xv[u][1].y + c[3] * inv_hi * w.y);
     }
   }
 }
@@ -222,7 +458,7 @@ template <typename S, int TOK, bool VEC>
 int launch_token_gated_update(float* h, const void* a, float sa, const void* b, float sb, const int* tokens,
                               const void* table, long long ld_table, int col0, const void* w_gate, const void* w_proj,
                               const float* norm_w, float eps, int T, int D, int R, cudaStream_t stream) {
-  const size_t smem = (static_cast<size_t>(2) * TOK * D + static_cast<size_t>(TOK) * R) * sizeof(float);
+  const size_t smem = (static_cast<size_t>(2) * TOK * D + static_cast<size_t>(2) * TOK * R) * sizeof(float);
   auto kern = token_gated_update_kernel<S, TOK, VEC>;
   if (smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -234,21 +470,53 @@ int launch_token_gated_update(float* h, const void* a, float sa, const void* b, 
   return launch_status();
 }
 
+template <int RK>
+int launch_token_gated_update_mma(float* h, const void* a, float sa, const void* b, float sb, const int* tokens,
+                                  const void* table, long long ld_table, int col0, const void* w_gate, const void* w_proj,
+                                  const float* norm_w, float eps, int T, int D, cudaStream_t stream) {
+  const size_t smem = side_mma_smem_bytes(D, 16 * RK);
+  auto kern = token_gated_update_mma_kernel<RK>;
+  if (smem > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return static_cast<int>(err);
+  }
+  launch_pdl(kern, dim3((T + kSideMmaTok - 1) / kSideMmaTok), dim3(kSideMmaThreads), smem, stream, h,
+             static_cast<const bf16*>(a), sa, static_cast<const bf16*>(b), sb, tokens, static_cast<const bf16*>(table),
+             ld_table, col0, static_cast<const bf16*>(w_gate), static_cast<const bf16*>(w_proj), norm_w, eps, T, D);
+  return launch_status();
+}
+
 }  // namespace pmm
 
 // How many floats of shared memory a block of `tok` tokens needs; the launcher takes 4 tokens a block where
 // the step has many tokens and they fit, else 1.
 PMM_EXPORT int pmm_token_gated_update_fits(int D, int R) {
-  return (static_cast<size_t>(2) * D + R) * sizeof(float) <= 200 * 1024 ? 1 : 0;
+  return (static_cast<size_t>(2) * D + 2 * static_cast<size_t>(R)) * sizeof(float) <= 200 * 1024 ? 1 : 0;
 }
 
+// w_proj: Wp^T [R, D].  w_proj_rows: Wp [D, R] as stored, or null; with it, bfloat16 steps of many tokens whose
+// sizes the tensor-core form takes (D a multiple of 16, R 16, 32 or 64) run that form.
 PMM_EXPORT int pmm_token_gated_update(float* h, const void* a, float sa, const void* b, float sb, const int* tokens,
                                       const void* table, long long ld_table, int col0, const void* w_gate,
-                                      const void* w_proj, const float* norm_w, float eps, int T, int D, int R, int dtype,
-                                      cudaStream_t stream) {
+                                      const void* w_proj, const void* w_proj_rows, const float* norm_w, float eps, int T,
+                                      int D, int R, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (D <= 0 || R <= 0 || col0 < 0 || !pmm_token_gated_update_fits(D, R)) return PMM_ERR_BAD_ARGUMENT;
-  const bool four = T >= 1024 && (static_cast<size_t>(8) * D + 4 * static_cast<size_t>(R)) * sizeof(float) <= 200 * 1024;
+  {
+    auto al = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    if (dtype == PMM_DTYPE_BF16 && w_proj_rows != nullptr && T >= pmm::kSideMmaFromTokens && D % 16 == 0 &&
+        (R == 16 || R == 32 || R == 64) && al(h) && al(a) && al(b) && al(w_gate) && al(w_proj_rows) && al(norm_w) &&
+        pmm::side_mma_smem_bytes(D, R) <= 200 * 1024) {
+#define PMM_SIDE_MMA(RK)                                                                                               \
+  return pmm::launch_token_gated_update_mma<RK>(h, a, sa, b, sb, tokens, table, ld_table, col0, w_gate, w_proj_rows, \
+                                                norm_w, eps, T, D, stream)
+      if (R == 16) PMM_SIDE_MMA(1);
+      if (R == 32) PMM_SIDE_MMA(2);
+      PMM_SIDE_MMA(4);
+#undef PMM_SIDE_MMA
+    }
+  }
+  const bool four = T >= 1024 && (static_cast<size_t>(8) * D + 8 * static_cast<size_t>(R)) * sizeof(float) <= 200 * 1024;
   auto aligned = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool vec = D % 4 == 0 && R % 4 == 0 && aligned(h) && aligned(a) && aligned(b) && aligned(w_gate) &&
                    aligned(w_proj) && aligned(norm_w);

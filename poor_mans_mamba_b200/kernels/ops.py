@@ -139,7 +139,7 @@ _SIGNATURES = {
                       c_void_p],
     "pmm_token_gated_update_fits": [c_int, c_int],
     "pmm_token_gated_update": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p, c_longlong, c_int,
-                               c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p],
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_cast_rows": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
     "pmm_relu_squared": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
     "pmm_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -1540,12 +1540,20 @@ def token_gated_update_fits(width: int, rank: int) -> bool:
 
 
 def token_gated_update(h: Tensor, branches: Sequence[Tuple[Tensor, float]], tokens: Tensor, table: Tensor, col0: int,
-                       w_gate: Tensor, w_proj_t: Tensor, norm_w: Tensor, eps: float) -> None:
+                       w_gate: Tensor, w_proj_t: Tensor, norm_w: Tensor, eps: float,
+                       w_proj_rows: Optional[Tensor] = None) -> None:
     """h <- x + rms(Wp (gelu_tanh(Wg x) * e)) * norm_w with x = h + sum(scale_i * branch_i) (at most two branches)
     and e = table[token, col0 : col0 + R]; h [T, D] float32 in place, Wg [R, D], Wp given transposed: Wp^T [R, D]
-    (its rows are then read side by side)."""
+    (its rows are then read side by side).  With ``w_proj_rows`` (Wp [D, R] as stored) bfloat16 steps of many
+    tokens run on the tensor cores where the sizes allow: x and g enter the two products rounded to bfloat16
+    there, sums, activation, root mean square and the stream stay float."""
     items = list(branches)
     w_proj = w_proj_t
+    if w_proj_rows is not None:
+        _cuda(w_proj_rows)
+        if not (w_proj_rows.shape == (w_proj_t.shape[1], w_proj_t.shape[0]) and w_proj_rows.is_contiguous()
+                and w_proj_rows.dtype == w_proj_t.dtype):
+            raise KernelError("token_gated_update: w_proj_rows must be contiguous [D, R] of the matrices' type")
     _cuda(h, tokens, table, w_gate, w_proj, norm_w, *[b for b, _ in items])
     T, D = h.shape
     R = w_gate.shape[0]
@@ -1564,7 +1572,7 @@ def token_gated_update(h: Tensor, branches: Sequence[Tuple[Tensor, float]], toke
     _i32(tokens, "token_gated_update: tokens")
     (a, sa), (b, sb) = (items + [(None, 0.0), (None, 0.0)])[:2]
     _call("pmm_token_gated_update", h.data_ptr(), _ptr(a), float(sa), _ptr(b), float(sb), tokens.data_ptr(), table.data_ptr(),
-          table.stride(0), int(col0), w_gate.data_ptr(), w_proj.data_ptr(), norm_w.data_ptr(), float(eps), T, D, R,
+          table.stride(0), int(col0), w_gate.data_ptr(), w_proj.data_ptr(), _ptr(w_proj_rows), norm_w.data_ptr(), float(eps), T, D, R,
           _dt(w_gate), _stream())
 
 

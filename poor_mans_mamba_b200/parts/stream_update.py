@@ -52,11 +52,12 @@ class TokenGatedUpdate(StreamUpdate):
         g, p, n = self.tensors
         self.table = params[self.table_name]
         self.w_gate, self.w_proj_t = params[g].contiguous(), params[p].t().contiguous()  # Wp^T [R, D]
+        self.w_proj = params[p].contiguous()  # as stored, for the tensor-core form
         self.norm_w = params[n].contiguous()
 
     def forward(self, stream, ctx) -> None:
         K.token_gated_update(stream.h, stream.take_pending(2), ctx.tokens, self.table, self.column, self.w_gate,
-                             self.w_proj_t, self.norm_w, self.eps)
+                             self.w_proj_t, self.norm_w, self.eps, w_proj_rows=self.w_proj)
 
 
 class EmbeddingReentry(StreamUpdate):

@@ -163,7 +163,8 @@ def test_latent_mixer_on_a_prompt_and_then_token_by_token(dtype, rotated, tmp_pa
 # ----------------------------------------------------------------------------- the token input and the re-entry
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("D,R,layers,layer,T", [(72, 6, 4, 2, 9), (100, 1, 3, 0, 9), (44, 3, 2, 1, 9), (384, 24, 3, 2, 9),
-                                                 (1031, 16, 2, 1, 9), (1024, 32, 2, 1, 9), (320, 16, 2, 0, 1030), (72, 6, 3, 1, 1027)])
+                                                 (1031, 16, 2, 1, 9), (1024, 32, 2, 1, 9), (320, 16, 2, 0, 1030), (72, 6, 3, 1, 1027),
+                                                 (1024, 32, 2, 1, 1100), (192, 64, 2, 0, 1025)])
 def test_token_input_with_waiting_branches(dtype, D, R, layers, layer, T):
     """Rows read one entry and four entries at a time, one token and four tokens a block (a step of many tokens, its
     last block short)."""
@@ -178,12 +179,14 @@ def test_token_input_with_waiting_branches(dtype, D, R, layers, layer, T):
     ad, bd = a.to(DEV, dtype), b.to(DEV, dtype)
     for branches, x in (([], h.double()), ([(ad, 1.0)], h.double() + ad.double().cpu()),
                         ([(ad, 1.0), (bd, 0.5)], h.double() + ad.double().cpu() + 0.5 * bd.double().cpu())):
-        hd = h.to(DEV).clone()
-        K.token_gated_update(hd, branches, tokens.to(DEV, torch.int32), table.to(DEV, dtype), layer * R, wg.to(DEV, dtype),
-                             wp.t().contiguous().to(DEV, dtype), nw.to(DEV), eps)
-        # the stream itself is float in both storage types; only the small products read rounded matrices
-        close(hd, P.token_input(x, tokens, W, layer, R, eps), torch.float32, f"token input, {len(branches)} branches",
-              f32=3e-5 if dtype == torch.float32 else 2e-2)
+        want = P.token_input(x, tokens, W, layer, R, eps)
+        # with the matrix as stored, bfloat16 steps of many tokens take the tensor-core form where the sizes allow
+        for rows in (None, wp.to(DEV, dtype)):
+            hd = h.to(DEV).clone()
+            K.token_gated_update(hd, branches, tokens.to(DEV, torch.int32), table.to(DEV, dtype), layer * R, wg.to(DEV, dtype),
+                                 wp.t().contiguous().to(DEV, dtype), nw.to(DEV), eps, w_proj_rows=rows)
+            # the stream itself is float in both storage types; only the small products read rounded operands
+            close(hd, want, torch.float32, f"token input, {len(branches)} branches", f32=3e-5 if dtype == torch.float32 else 2e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
