@@ -49,15 +49,26 @@ __global__ void __launch_bounds__(kSideThreads)
   float* gs = ys + static_cast<size_t>(TOK) * D;
   float* es = gs + TOK * R;
   pdl_launch_dependents();
-  pdl_wait();
   const int t0 = blockIdx.x * TOK;
   const int nt = min(TOK, T - t0);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  // the tokens' table entries, fetched beside the rows of the stream (two dependent reads a token, all in flight at once)
+  // What does not depend on the launch before this one is asked for while that one still runs: the two matrices
+  // towards the L2 (the blocks share out their 128-byte lines) and the tokens' table entries (two dependent
+  // reads a token, all in flight at once).
+  {
+    const int lines = static_cast<int>((static_cast<size_t>(R) * D * sizeof(S)) >> 7);  // per matrix
+    const int each = min(kSideThreads, (lines + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x));
+    if (static_cast<int>(threadIdx.x) < each) {
+      const size_t line = static_cast<size_t>((blockIdx.x * each + threadIdx.x) % lines) << 7;
+      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(reinterpret_cast<const char*>(w_gate) + line));
+      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(reinterpret_cast<const char*>(w_proj_t) + line));
+    }
+  }
   for (int idx = threadIdx.x; idx < TOK * R; idx += kSideThreads) {
     const int r = idx / R, j = idx - r * R;
     es[idx] = r < nt ? ldf(table + static_cast<long long>(tokens[t0 + r]) * ld_table + col0 + j) : 0.f;
   }
+  pdl_wait();
   // x = h + sa * a + sb * b; the rows of a short last block that have no token are zero
   if (VEC) {
     const int per_row = D >> 2;
@@ -104,7 +115,7 @@ __global__ void __launch_bounds__(kSideThreads)
 #pragma unroll
         for (int r = 0; r < TOK; ++r) acc[q][r] = 0.f;
       const S* wr = w_gate + static_cast<size_t>(j0) * D;
-#pragma unroll 2
+#pragma unroll(TOK == 1 ? 4 : 2)
       for (int i = lane << 2; i < D; i += 128) {
         float4 w[4];
 #pragma unroll
