@@ -310,3 +310,59 @@ def test_medium_sizes_where_the_tensor_core_forms_run(tmp_path):
             out = H.run_script(runner, seqs, script)
             for i, ref in enumerate(refs):
                 check_rows(out[i], ref, dtype, f"medium {dtype} {name} seq {i}", f32_frac=4e-5)
+
+
+def _random_config(seed):
+    """A configuration drawn at random from the ranges a small model of this design may take: every size, the
+    order of the layers, the loop, the router's groups and the token input."""
+    import random
+    rng = random.Random(1000 + seed)
+    layers = []
+    for _ in range(rng.randint(2, 5)):
+        dim = rng.choice([16, 32, 48, 64, 80, 128])
+        mixer = {"heads": rng.randint(1, 12), "dim": dim, "vdim": rng.choice([16, 32, 64, 96, 128]),
+                 "q_rank": 8 * rng.randint(3, 20), "kv_rank": rng.choice([16, 32, 48, 64, 96, 128, 160, 192]), "scale": 0.0}
+        if rng.random() < 0.5:
+            rd = rng.choice([8, 16, 32, 64])
+            mixer.update({"rot_dim": rd, "rot": {"dims": rng.choice([rd, rd, rd // 2]), "base": rng.choice([100.0, 1e4, 5e5])}})
+        mixer["scale"] = (dim + mixer.get("rot_dim", 0)) ** -0.5
+        kind = rng.choice(["dense", "moe", "moe", None])
+        mlp = None
+        if kind == "dense":
+            mlp = {"kind": "dense", "ff": 8 * rng.randint(8, 60)}
+        elif kind == "moe":
+            experts = rng.choice([4, 6, 8, 12, 16])
+            count = rng.choice([c for c in (1, 2, 3, 4, experts) if experts % c == 0])
+            keep = rng.randint(1, count)
+            router = {"experts": experts, "top": rng.randint(1, min(6, keep * (experts // count)))}
+            if count > 1 or rng.random() < 0.5:
+                router["groups"] = {"count": count, "keep": keep}
+            if rng.random() < 0.7:
+                router["scale"] = rng.choice([0.5, 1.5, 2.0, 2.5])
+            mlp = {"kind": "moe", "router": router, "expert": {"ff": 8 * rng.randint(2, 16)}}
+            if rng.random() < 0.7:
+                mlp["shared"] = {"ff": 8 * rng.randint(2, 24)}
+        layers.append({"type": "latent_attention_2" if "rot_dim" in mixer else "latent_attention", "mixer": mixer, "mlp": mlp})
+    cfg = {"architecture": "Gikovik", "vocab": rng.randint(100, 700), "width": rng.choice([96, 136, 160, 200, 256, 328]),
+           "norm": {"eps": rng.choice([1e-6, 1e-5])}, "layers": layers}
+    if rng.random() < 0.7:
+        start = rng.randrange(len(layers))
+        cfg["loop"] = {"start": start, "stop": rng.randint(start + 1, len(layers)), "times": rng.randint(1, 3)}
+    if rng.random() < 0.7:
+        cfg["token_side"] = {"dim": rng.choice([4, 8, 16, 24, 32])}
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    cfg = _random_config(seed)
+    case = Case(cfg, tmp_path, lengths=(150, 37, 70), seq_seed=seed, seed=50 + seed)
+    seqs = case.seqs
+    for dtype in ("float32", "bfloat16"):
+        d, weights, refs = case.of(dtype)
+        for name, script in (("whole", H.script_whole(seqs)),
+                             ("mixed", H.script_mixed(seqs, max_live=3, seed=seed, budget_pages=8, page_size=64))):
+            runner = H.make_runner(d, dtype, page_size=64, num_pages=8, num_slots=3)
+            out = H.run_script(runner, seqs, script)
+            for i, ref in enumerate(refs):
+                check_rows(out[i], ref, dtype, f"random {seed} {dtype} {name} seq {i}: {json.dumps(cfg)[:300]}", f32_frac=4e-5)
