@@ -239,28 +239,31 @@ __global__ void __launch_bounds__(kSideThreads)
 // shared memory.  Wp g: the warps split the columns; the tiles are made twice (K is only R), first for the
 // sum of squares and then for the stream, so that no row of y waits anywhere, whatever D is.
 constexpr int kSideMmaThreads = 512, kSideMmaWarps = kSideMmaThreads / 32, kSideMmaTok = 16;
+constexpr int kSideStage = 33;  // floats a row of a warp's staged 16 x 32 piece of y
 constexpr int kSideMmaFromTokens = 1024;  // below, a block per token on the CUDA cores fills the SMs better
 
 inline size_t side_mma_smem_bytes(int D, int R) {
-  return static_cast<size_t>(kSideMmaTok) * (D + 8) * 2 + static_cast<size_t>(kSideMmaWarps) * kSideMmaTok * R * 4 +
+  const size_t per_warp = static_cast<size_t>(R > kSideStage ? R : kSideStage) * kSideMmaTok;
+  return static_cast<size_t>(kSideMmaTok) * (D + 32) * 2 + static_cast<size_t>(kSideMmaWarps) * per_warp * 4 +
          static_cast<size_t>(kSideMmaTok) * R * 4 + static_cast<size_t>(kSideMmaWarps) * kSideMmaTok * 4 +
-         static_cast<size_t>(kSideMmaTok) * (R + 8) * 2;
+         static_cast<size_t>(kSideMmaTok) * 4 + static_cast<size_t>(kSideMmaTok) * (R + 8) * 2;
 }
 
 template <int RK>
-__global__ void __launch_bounds__(kSideMmaThreads)
+__global__ void __launch_bounds__(kSideMmaThreads)  // (64 registers for two blocks an SM, and 256 threads a block, measured slower)
     token_gated_update_mma_kernel(float* __restrict__ h, const bf16* __restrict__ a, float sa, const bf16* __restrict__ b,
                                   float sb, const int* __restrict__ tokens, const bf16* __restrict__ table,
                                   long long ld_table, int col0, const bf16* __restrict__ w_gate,
                                   const bf16* __restrict__ w_proj, const float* __restrict__ norm_w, float eps, int T, int D) {
-  constexpr int R = 16 * RK, NT1 = 2 * RK, GS = R + 8;
+  constexpr int R = 16 * RK, NT1 = 2 * RK, GS = R + 8, PW = (R > kSideStage ? R : kSideStage) * kSideMmaTok;
   extern __shared__ __align__(16) unsigned char side_mma_smem[];
-  const int XS = D + 8;                                             // row stride of xb: rows fall into different banks
-  bf16* xb = reinterpret_cast<bf16*>(side_mma_smem);                // [16][D + 8]
-  float* part = reinterpret_cast<float*>(xb + kSideMmaTok * XS);    // [warps][16][R]
-  float* es = part + kSideMmaWarps * kSideMmaTok * R;               // [16][R]
+  const int XS = D + 32;                                            // row stride of xb: neighbouring rows 64 bytes apart in the banks
+  bf16* xb = reinterpret_cast<bf16*>(side_mma_smem);                // [16][D + 32]
+  float* part = reinterpret_cast<float*>(xb + kSideMmaTok * XS);    // [warps][16][R], later [warps][16][33] (a warp's staged tiles)
+  float* es = part + kSideMmaWarps * PW;                            // [16][R]
   float* sqs = es + kSideMmaTok * R;                                // [warps][16]
-  bf16* gb = reinterpret_cast<bf16*>(sqs + kSideMmaWarps * kSideMmaTok);  // [16][R + 8]
+  float* invs = sqs + kSideMmaWarps * kSideMmaTok;                  // [16]
+  bf16* gb = reinterpret_cast<bf16*>(invs + kSideMmaTok);           // [16][R + 8]
   pdl_launch_dependents();
   const int t0 = blockIdx.x * kSideMmaTok;
   const int nt = min(kSideMmaTok, T - t0);
@@ -303,29 +306,30 @@ __global__ void __launch_bounds__(kSideMmaThreads)
     *reinterpret_cast<uint2*>(xb + r * XS + i) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
   }
   __syncthreads();
+  // In both products a lane reads its operands in 16-byte pieces of one row, so the order of the summed index
+  // inside a product step differs from the instruction's own; it is the same on both sides, which is all a sum
+  // needs.  Slices of 32 of D here: lane (g, t) holds entries t * 8 .. t * 8 + 7 of its rows of x and of Wg.
   {  // part[warp] = x[:, this warp's slices of D] Wg[:, the same]^T
     float acc[NT1][4];
 #pragma unroll
     for (int n = 0; n < NT1; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
 #pragma unroll 2
-    for (int k0 = warp * 16; k0 < D; k0 += kSideMmaWarps * 16) {
-      const bf16* xr = xb + g * XS + k0 + 2 * t;
-      unsigned af[4];
-      af[0] = *reinterpret_cast<const unsigned*>(xr);
-      af[1] = *reinterpret_cast<const unsigned*>(xr + 8 * XS);
-      af[2] = *reinterpret_cast<const unsigned*>(xr + 8);
-      af[3] = *reinterpret_cast<const unsigned*>(xr + 8 * XS + 8);
-      unsigned bf[NT1][2];
+    for (int k0 = warp * 32; k0 < D; k0 += kSideMmaWarps * 32) {
+      const bf16* xr = xb + g * XS + k0 + t * 8;
+      const uint4 lo = *reinterpret_cast<const uint4*>(xr);
+      const uint4 hi = *reinterpret_cast<const uint4*>(xr + 8 * XS);
+      const unsigned a0[4] = {lo.x, hi.x, lo.y, hi.y}, a1[4] = {lo.z, hi.z, lo.w, hi.w};
+      uint4 bw[NT1];
+#pragma unroll
+      for (int n = 0; n < NT1; ++n)
+        bw[n] = *reinterpret_cast<const uint4*>(w_gate + static_cast<size_t>(n * 8 + g) * D + k0 + t * 8);
 #pragma unroll
       for (int n = 0; n < NT1; ++n) {
-        const bf16* wr = w_gate + static_cast<size_t>(n * 8 + g) * D + k0 + 2 * t;
-        bf[n][0] = *reinterpret_cast<const unsigned*>(wr);
-        bf[n][1] = *reinterpret_cast<const unsigned*>(wr + 8);
+        mma_bf16(acc[n], a0, bw[n].x, bw[n].y);
+        mma_bf16(acc[n], a1, bw[n].z, bw[n].w);
       }
-#pragma unroll
-      for (int n = 0; n < NT1; ++n) mma_bf16(acc[n], af, bf[n][0], bf[n][1]);
     }
-    float* mine = part + warp * kSideMmaTok * R;
+    float* mine = part + warp * PW;
 #pragma unroll
     for (int n = 0; n < NT1; ++n) {
       *reinterpret_cast<float2*>(mine + g * R + n * 8 + 2 * t) = make_float2(acc[n][0], acc[n][1]);
@@ -336,40 +340,49 @@ __global__ void __launch_bounds__(kSideMmaThreads)
   for (int idx = threadIdx.x; idx < kSideMmaTok * R; idx += kSideMmaThreads) {
     float sum = 0.f;
 #pragma unroll
-    for (int w = 0; w < kSideMmaWarps; ++w) sum += part[w * kSideMmaTok * R + idx];
+    for (int w = 0; w < kSideMmaWarps; ++w) sum += part[w * PW + idx];
     const int r = idx / R, j = idx - r * R;
     gb[r * GS + j] = __float2bfloat16_rn(gelu_tanh_f(sum) * es[idx]);
   }
   __syncthreads();
+  // Wp g: a tile's eight rows of Wp are 16 R bytes in a row; lane L reads bytes L * R / 2 .. of them, which are
+  // entries t * 4 RK .. of row g, and takes the same entries of g_r on the other side.
   unsigned ga[RK][4];
 #pragma unroll
   for (int kk = 0; kk < RK; ++kk) {
-    const bf16* gr = gb + g * GS + kk * 16 + 2 * t;
+    const bf16* gr = gb + g * GS + t * 4 * RK + 4 * kk;
     ga[kk][0] = *reinterpret_cast<const unsigned*>(gr);
     ga[kk][1] = *reinterpret_cast<const unsigned*>(gr + 8 * GS);
-    ga[kk][2] = *reinterpret_cast<const unsigned*>(gr + 8);
-    ga[kk][3] = *reinterpret_cast<const unsigned*>(gr + 8 * GS + 8);
+    ga[kk][2] = *reinterpret_cast<const unsigned*>(gr + 2);
+    ga[kk][3] = *reinterpret_cast<const unsigned*>(gr + 8 * GS + 2);
   }
   auto y_tile = [&](int tile, float* c) {
     c[0] = c[1] = c[2] = c[3] = 0.f;
-    const bf16* wr = w_proj + static_cast<size_t>(tile * 8 + g) * R + 2 * t;
-    unsigned bf[RK][2];
+    const bf16* wr = w_proj + static_cast<size_t>(tile) * 8 * R + lane * 4 * RK;
+    unsigned bw[2 * RK];
+    if (RK == 1) {
+      const uint2 v = *reinterpret_cast<const uint2*>(wr);
+      bw[0] = v.x, bw[1] = v.y;
+    } else {
 #pragma unroll
-    for (int kk = 0; kk < RK; ++kk) {
-      bf[kk][0] = *reinterpret_cast<const unsigned*>(wr + kk * 16);
-      bf[kk][1] = *reinterpret_cast<const unsigned*>(wr + kk * 16 + 8);
+      for (int q = 0; q < RK / 2; ++q) {
+        const uint4 v = reinterpret_cast<const uint4*>(wr)[q];
+        bw[4 * q] = v.x, bw[4 * q + 1] = v.y, bw[4 * q + 2] = v.z, bw[4 * q + 3] = v.w;
+      }
     }
 #pragma unroll
-    for (int kk = 0; kk < RK; ++kk) mma_bf16(c, ga[kk], bf[kk][0], bf[kk][1]);
+    for (int kk = 0; kk < RK; ++kk) mma_bf16(c, ga[kk], bw[2 * kk], bw[2 * kk + 1]);
   };
-  const int tiles = D >> 3;
+  const int blocks32 = D >> 5;  // a warp takes blocks of 32 columns: four tiles
   float sq_lo = 0.f, sq_hi = 0.f;
-#pragma unroll 4
-  for (int tile = warp; tile < tiles; tile += kSideMmaWarps) {
-    float c[4];
-    y_tile(tile, c);
-    sq_lo += c[0] * c[0] + c[1] * c[1];
-    sq_hi += c[2] * c[2] + c[3] * c[3];
+  for (int cb = warp; cb < blocks32; cb += kSideMmaWarps) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float c[4];
+      y_tile(cb * 4 + u, c);
+      sq_lo += c[0] * c[0] + c[1] * c[1];
+      sq_hi += c[2] * c[2] + c[3] * c[3];
+    }
   }
   sq_lo += __shfl_xor_sync(0xffffffffu, sq_lo, 1);
   sq_lo += __shfl_xor_sync(0xffffffffu, sq_lo, 2);
@@ -380,57 +393,49 @@ __global__ void __launch_bounds__(kSideMmaThreads)
     sqs[warp * kSideMmaTok + g + 8] = sq_hi;
   }
   __syncthreads();
-  float tot_lo = 0.f, tot_hi = 0.f;
+  if (threadIdx.x < kSideMmaTok) {
+    float total = 0.f;
 #pragma unroll
-  for (int w = 0; w < kSideMmaWarps; ++w) {
-    tot_lo += sqs[w * kSideMmaTok + g];
-    tot_hi += sqs[w * kSideMmaTok + g + 8];
+    for (int w = 0; w < kSideMmaWarps; ++w) total += sqs[w * kSideMmaTok + threadIdx.x];
+    invs[threadIdx.x] = 1.f / sqrtf(total / static_cast<float>(D) + eps);
   }
-  const float inv_lo = 1.f / sqrtf(tot_lo / static_cast<float>(D) + eps);
-  const float inv_hi = 1.f / sqrtf(tot_hi / static_cast<float>(D) + eps);
-  auto x_at = [&](int row, int col) {  // the stream with its branches at (row, col) and (row, col + 1)
-    float2 x = make_float2(0.f, 0.f);
-    if (row < nt) {
-      const size_t at = static_cast<size_t>(t0 + row) * D + col;
-      x = *reinterpret_cast<const float2*>(h + at);
-      if (a) {
-        const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(a + at));
-        x.x += sa * u.x, x.y += sa * u.y;
-      }
-      if (b) {
-        const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(b + at));
-        x.x += sb * u.x, x.y += sb * u.y;
-      }
-    }
-    return x;
-  };
-  // four tiles a turn: their reads of the stream are asked for together, before the first of their writes (the
-  // writes go to the array the reads come from, so the compiler keeps their order)
-  for (int tile0 = warp; tile0 < tiles; tile0 += 4 * kSideMmaWarps) {
-    float2 xv[4][2];
+  __syncthreads();
+  // The tiles once more, staged in shared memory so that the stream is read and written in whole rows of 32
+  // columns; eight rows' reads are asked for before the first of their writes (the writes go to the array the
+  // reads come from, so the compiler keeps their order).
+  float* st = part + warp * PW;  // [16][33]
+  for (int cb = warp; cb < blocks32; cb += kSideMmaWarps) {
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int tile = tile0 + u * kSideMmaWarps;
-      if (tile < tiles) {
-        xv[u][0] = x_at(g, tile * 8 + 2 * t);
-        xv[u][1] = x_at(g + 8, tile * 8 + 2 * t);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int tile = tile0 + u * kSideMmaWarps;
-      if (tile >= tiles) continue;
       float c[4];
-      y_tile(tile, c);
-      const int col = tile * 8 + 2 * t;
-      const float2 w = *reinterpret_cast<const float2*>(norm_w + col);
-      if (g < nt)
-        *reinterpret_cast<float2*>(h + static_cast<size_t>(t0 + g) * D + col) =
-            make_float2(xv[u][0].x + c[0] * inv_lo * w.x, xv[u][0].y + c[1] * inv_lo * w.y);
-      if (g + 8 < nt)
-        *reinterpret_cast<float2*>(h + static_cast<size_t>(t0 + g + 8) * D + col) =
-            make_float2(xv[u][1].x + c[2] * inv_hi * w.x, xv[u][1].y + c[3] * inv_hi * w.y);
+      y_tile(cb * 4 + u, c);
+      st[g * kSideStage + u * 8 + 2 * t] = c[0];
+      st[g * kSideStage + u * 8 + 2 * t + 1] = c[1];
+      st[(g + 8) * kSideStage + u * 8 + 2 * t] = c[2];
+      st[(g + 8) * kSideStage + u * 8 + 2 * t + 1] = c[3];
     }
+    __syncwarp();
+    const int col = cb * 32 + lane;
+    const float w = norm_w[col];
+#pragma unroll
+    for (int r0 = 0; r0 < kSideMmaTok; r0 += 8) {
+      float x[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        x[r] = 0.f;
+        if (r0 + r < nt) {
+          const size_t at = static_cast<size_t>(t0 + r0 + r) * D + col;
+          x[r] = h[at];
+          if (a) x[r] += sa * __bfloat162float(a[at]);
+          if (b) x[r] += sb * __bfloat162float(b[at]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r0 + r < nt)
+          h[static_cast<size_t>(t0 + r0 + r) * D + col] = x[r] + st[(r0 + r) * kSideStage + lane] * invs[r0 + r] * w;
+    }
+    __syncwarp();
   }
 }
 
@@ -506,7 +511,7 @@ PMM_EXPORT int pmm_token_gated_update_fits(int D, int R) {
 }
 
 // w_proj: Wp^T [R, D].  w_proj_rows: Wp [D, R] as stored, or null; with it, bfloat16 steps of many tokens whose
-// sizes the tensor-core form takes (D a multiple of 16, R 16, 32 or 64) run that form.
+// sizes the tensor-core form takes (D a multiple of 32, R 16, 32 or 64) run that form.
 PMM_EXPORT int pmm_token_gated_update(float* h, const void* a, float sa, const void* b, float sb, const int* tokens,
                                       const void* table, long long ld_table, int col0, const void* w_gate,
                                       const void* w_proj, const void* w_proj_rows, const float* norm_w, float eps, int T,
@@ -515,7 +520,7 @@ PMM_EXPORT int pmm_token_gated_update(float* h, const void* a, float sa, const v
   if (D <= 0 || R <= 0 || col0 < 0 || !pmm_token_gated_update_fits(D, R)) return PMM_ERR_BAD_ARGUMENT;
   {
     auto al = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
-    if (dtype == PMM_DTYPE_BF16 && w_proj_rows != nullptr && T >= pmm::kSideMmaFromTokens && D % 16 == 0 &&
+    if (dtype == PMM_DTYPE_BF16 && w_proj_rows != nullptr && T >= pmm::kSideMmaFromTokens && D % 32 == 0 &&
         (R == 16 || R == 32 || R == 64) && al(h) && al(a) && al(b) && al(w_gate) && al(w_proj_rows) && al(norm_w) &&
         pmm::side_mma_smem_bytes(D, R) <= 200 * 1024) {
 #define PMM_SIDE_MMA(RK)                                                                                               \
