@@ -5,7 +5,8 @@ Layers declare what they keep (StateSpec).  Paged states with the same row layou
 window form a *group*: the group has pages of its own ([member, page, plane, page_size,
 width] on the device, one member per layer state) and one block table per request, shared
 by the group's layers.  A group that only ever reads a window of the sequence gives pages
-back as soon as the window has passed them.  Fixed states live in slots ([slot, *shape]
+back as soon as the window has passed them (all but the pages that hold the first tokens, where
+the group's layers keep those visible).  Fixed states live in slots ([slot, *shape]
 per layer state; the states of one shape and dtype are slices of one tensor, so that admitting a
 request zeroes its slot in all layers with one fill per kind: 72 fills of the 36-layer model cost
 the host 0.5 ms per admitted request).  Everything a request holds is given back when it
@@ -48,9 +49,11 @@ class _Member:
 class PagedGroup:
     """Pages and block tables of the layer states that share one row layout and window."""
 
-    def __init__(self, key: Tuple, planes: int, width: int, window: int, page_size: int, num_pages: int):
+    def __init__(self, key: Tuple, planes: int, width: int, window: int, page_size: int, num_pages: int,
+                 keep_first: int = 0):
         self.key = key
         self.planes, self.width, self.window = planes, width, window
+        self.keep_first = keep_first if window > 0 else 0
         self.page_size, self.num_pages = page_size, num_pages
         self.members: List[_Member] = []
         self.pool = PagePool(num_pages)
@@ -65,6 +68,10 @@ class PagedGroup:
         if self.window <= 0:
             return 0
         return max(0, next_pos - self.window + 1) // self.page_size
+
+    def kept_blocks(self) -> int:
+        """The logical blocks at the start of a request that are never given back."""
+        return self.blocks_for(self.keep_first)
 
     def pages_to_grow(self, req: Hashable, new_len: int) -> int:
         return max(0, self.blocks_for(new_len) - len(self.tables.get(req, [])))
@@ -85,10 +92,12 @@ class CacheManager:
             for name, spec in specs:
                 if spec.kind == "paged":
                     key = (spec.planes, spec.width, spec.window)
+                    if spec.window > 0 and spec.keep_first > 0:
+                        key += (spec.keep_first,)
                     if key not in self.groups:
                         n = (pages_per_group or {}).get(key, num_pages)
                         self.groups[key] = PagedGroup(key, spec.planes, spec.width, spec.window,
-                                                      self.page_size, int(n))
+                                                      self.page_size, int(n), spec.keep_first)
                     g = self.groups[key]
                     self._paged_of[(layer, name)] = (g, len(g.members))
                     g.members.append(_Member(layer, name))
@@ -167,7 +176,7 @@ class CacheManager:
             if g.window <= 0:
                 continue
             table = g.tables[req]
-            for b in range(min(g.first_needed_block(cur_len), len(table))):
+            for b in range(g.kept_blocks(), min(g.first_needed_block(cur_len), len(table))):
                 if table[b] >= 0:
                     g.pool.free(table[b], req)
                     table[b] = -1

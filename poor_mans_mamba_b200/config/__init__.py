@@ -2,6 +2,7 @@ from .base import ConfigError, KeyReader, load_config_json
 from .boketar import BoketarConfig
 from .tafesun import TafesunConfig
 from .gikovik import GikovikConfig
+from .sorovik import SorovikConfig
 from .falcon_h1 import AttentionConfig, FalconH1Config, Mamba2Config, Multipliers
 from .registry import (Architecture, open_model_dir, register_architecture, registered_architectures,
                        resolve_architecture)

@@ -5,8 +5,9 @@
 // for the scores, one slice of the head dimension per lane for the value sum) with an
 // online softmax.  Portions of prompts and decoded tokens are the same to it: a token at
 // absolute position pos sees keys lo..pos of its own request through the block table;
-// lo = pos-window+1 for a sliding window, else 0.  With one split the result is written
-// normalised; with several, (max, sum, unnormalised output) go to scratch and
+// lo = pos-window+1 for a sliding window, else 0; with keep_first the first keep_first keys of the
+// request stay visible behind the window (a second key range, at their true positions).  With one
+// split the result is written normalised; with several, (max, sum, unnormalised output) go to scratch and
 // flash_combine (attention_mma.cu) merges them.  This kernel is the 32-bit path and the general
 // fallback of the bfloat16 path; the tensor-core kernels cover the long cases.
 //
@@ -57,7 +58,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
                            S* __restrict__ out, float* __restrict__ part_o,
                            float* __restrict__ part_ml, float scale, int window, int split_len,
                            int n_splits, int page_size, int Hq, int Hkv, int Dh,
-                           const float* __restrict__ sink) {
+                           const float* __restrict__ sink, int keep_first) {
   extern __shared__ float qs[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -67,9 +68,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   const int hk = hq / (Hq / Hkv);
   const int pos = positions[t];
   const int* bt = block_table + static_cast<size_t>(seq_of[t]) * max_blocks;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int k_begin = max(lo, z * split_len);
+  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  if (lo <= keep_first) lo = 0;  // the kept first keys and the window are one range
   const int k_end = min(pos + 1, (z + 1) * split_len);
+  // two key ranges within this split: the kept first keys (empty unless the window has left them), then the window
+  const int r_begin[2] = {z * split_len, max(lo, z * split_len)};
+  const int r_end[2] = {lo > 0 ? min(keep_first, k_end) : 0, k_end};
   const int kv_dim = Hkv * Dh;
   const long long v_plane = static_cast<long long>(page_size) * kv_dim;
 
@@ -83,33 +87,36 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
 #pragma unroll
   for (int i = 0; i < kAttnMaxAcc; ++i) acc[i] = 0.f;
 
-  for (int base = k_begin; base < k_end; base += 32) {
-    const int key = base + lane;
-    const bool valid = key < k_end;
-    long long koff = 0;
-    float sc = -CUDART_INF_F;
-    if (valid) {
-      const int page = bt[key / page_size];
-      koff = (static_cast<long long>(page) * 2 * page_size + key % page_size) * kv_dim + hk * Dh;
-      sc = dot_row(qw, pool + koff, Dh) * scale;
-    }
-    const float m_new = fmaxf(m, warp_max(sc));  // lane 0 is always valid, so m_new is finite
-    const float p = valid ? expf(sc - m_new) : 0.f;
-    const float corr = expf(m - m_new);  // first chunk: exp(-inf) = 0
-    l = l * corr + warp_sum(p);
-#pragma unroll
-    for (int i = 0; i < kAttnMaxAcc; ++i) acc[i] *= corr;
-    const int n_valid = min(32, k_end - base);
-    for (int j = 0; j < n_valid; ++j) {
-      const float pj = __shfl_sync(0xffffffffu, p, j);
-      const long long voff = __shfl_sync(0xffffffffu, koff, j) + v_plane;
-#pragma unroll
-      for (int i = 0; i < kAttnMaxAcc; ++i) {
-        const int d = lane + 32 * i;
-        if (d < Dh) acc[i] += pj * ldf(pool + voff + d);
+  for (int range = 0; range < 2; ++range) {
+  const int k_begin = r_begin[range], k_end = r_end[range];
+    for (int base = k_begin; base < k_end; base += 32) {
+      const int key = base + lane;
+      const bool valid = key < k_end;
+      long long koff = 0;
+      float sc = -CUDART_INF_F;
+      if (valid) {
+        const int page = bt[key / page_size];
+        koff = (static_cast<long long>(page) * 2 * page_size + key % page_size) * kv_dim + hk * Dh;
+        sc = dot_row(qw, pool + koff, Dh) * scale;
       }
+      const float m_new = fmaxf(m, warp_max(sc));  // lane 0 is always valid, so m_new is finite
+      const float p = valid ? expf(sc - m_new) : 0.f;
+      const float corr = expf(m - m_new);  // first chunk: exp(-inf) = 0
+      l = l * corr + warp_sum(p);
+  #pragma unroll
+      for (int i = 0; i < kAttnMaxAcc; ++i) acc[i] *= corr;
+      const int n_valid = min(32, k_end - base);
+      for (int j = 0; j < n_valid; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, p, j);
+        const long long voff = __shfl_sync(0xffffffffu, koff, j) + v_plane;
+  #pragma unroll
+        for (int i = 0; i < kAttnMaxAcc; ++i) {
+          const int d = lane + 32 * i;
+          if (d < Dh) acc[i] += pj * ldf(pool + voff + d);
+        }
+      }
+      m = m_new;
     }
-    m = m_new;
   }
 
   if (sink && z == 0) {
@@ -150,12 +157,14 @@ PMM_EXPORT int pmm_paged_attention(const void* q, const void* pool, const int* b
                                    int max_blocks, const int* positions, const int* seq_of,
                                    void* out, float* part_o, float* part_ml, float scale, int window,
                                    int split_len, int n_splits, int page_size, int T, int Hq,
-                                   int Hkv, int Dh, int dtype, const float* sink, cudaStream_t stream) {
+                                   int Hkv, int Dh, int dtype, const float* sink, int keep_first,
+                                   cudaStream_t stream) {
   if (T <= 0) return 0;
   if (Dh <= 0 || Dh % 16 || Dh > 32 * pmm::kAttnMaxAcc) return PMM_ERR_BAD_ARGUMENT;
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || page_size <= 0 || n_splits < 1 || n_splits > 65535)
     return PMM_ERR_BAD_ARGUMENT;
   if (n_splits > 1 && (!part_o || !part_ml || split_len <= 0)) return PMM_ERR_BAD_ARGUMENT;
+  if (keep_first < 0) return PMM_ERR_BAD_ARGUMENT;
   if (n_splits == 1) split_len = 0x40000000;
   const int head_blocks = (Hq + pmm::kAttnWarps - 1) / pmm::kAttnWarps;
   if (head_blocks > 65535) return PMM_ERR_BAD_ARGUMENT;
@@ -165,7 +174,7 @@ PMM_EXPORT int pmm_paged_attention(const void* q, const void* pool, const int* b
     pmm::paged_attention_kernel<S><<<grid, pmm::kAttnWarps * 32, smem, stream>>>(
         static_cast<const S*>(q), static_cast<const S*>(pool), block_table, max_blocks, positions,
         seq_of, static_cast<S*>(out), part_o, part_ml, scale, window, split_len, n_splits,
-        page_size, Hq, Hkv, Dh, sink);
+        page_size, Hq, Hkv, Dh, sink, keep_first);
   });
   return pmm::launch_status();
 }

@@ -10,9 +10,13 @@
 
 namespace pmm {
 
+// norm_w != nullptr: the row is divided by its root mean square and multiplied by norm_w,
+//   h[t] = r / sqrt(mean(r^2) + eps) * norm_w with r = mult * E[tok[t]], all in float.
 template <typename S>
 __global__ void embed_kernel(float* __restrict__ out, const S* __restrict__ table,
-                             const int* __restrict__ tokens, float mult, int D, int V) {
+                             const int* __restrict__ tokens, float mult, int D, int V,
+                             const float* __restrict__ norm_w, float eps) {
+  __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -21,7 +25,17 @@ __global__ void embed_kernel(float* __restrict__ out, const S* __restrict__ tabl
   if (!ok) id = 0;
   const S* row = table + static_cast<size_t>(id) * D;
   float* o = out + static_cast<size_t>(t) * D;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = ok ? mult * ldf(row + i) : 0.f;
+  if (!norm_w) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = ok ? mult * ldf(row + i) : 0.f;
+    return;
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float v = ok ? mult * ldf(row + i) : 0.f;
+    ss += v * v;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(D) + eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = ok ? mult * ldf(row + i) * inv * norm_w[i] : 0.f;
 }
 
 // One block per output row.  h' = (h + sa*a) + sb*b ; out = h' * rsqrt(mean(h'^2)+eps) * w.
@@ -107,6 +121,52 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const S* __restric
   }
 }
 
+// A sublayer's result is normed once more before it joins the stream, and the stream is normed for the
+// next sublayer, in one launch (a block per row, the row kept in shared memory, float throughout):
+//   s   = sa * a + sb * b
+//   u   = s / sqrt(mean(s^2) + post_eps) * post_w
+//   v   = h + u                      (h absent: v = u);  h = v when rows == nullptr
+//   out = v / sqrt(mean(v^2) + eps) * w          (when out is given; w absent: out = v)
+// rows != nullptr: h is left untouched and out[r] comes from row rows[r] of h, a and b.
+template <typename S>
+__global__ void add_postnorm_rmsnorm_kernel(float* __restrict__ h, const S* __restrict__ a, float sa,
+                                            const S* __restrict__ b, float sb, const float* __restrict__ post_w,
+                                            float post_eps, const float* __restrict__ w, float eps,
+                                            S* __restrict__ out, const int* __restrict__ rows, int D) {
+  extern __shared__ float buf[];
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const size_t src = static_cast<size_t>(rows ? rows[r] : r) * D;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float s = sa * ldf(a + src + i);
+    if (b) s = s + sb * ldf(b + src + i);
+    buf[i] = s;
+    ss += s * s;
+  }
+  const float inv_p = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(D) + post_eps);
+  float sv = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = buf[i] * inv_p * post_w[i];
+    if (h) {
+      v = h[src + i] + v;
+      if (!rows) h[src + i] = v;
+    }
+    buf[i] = v;
+    sv += v * v;
+  }
+  if (!out) return;
+  S* o = out + static_cast<size_t>(r) * D;
+  if (!w) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) stf(o + i, buf[i]);
+    return;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sv, red) / static_cast<float>(D) + eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) stf(o + i, buf[i] * inv * w[i]);
+}
+
 __global__ void scale_f32_kernel(float* __restrict__ x, float s, size_t n) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) x[i] *= s;
@@ -121,11 +181,11 @@ __global__ void cast_scale_kernel(float* __restrict__ out, const S* __restrict__
 }  // namespace pmm
 
 PMM_EXPORT int pmm_embed(void* out, const void* table, const int* tokens, float mult, int T, int D,
-                         int V, int dtype, cudaStream_t stream) {
+                         int V, int dtype, const float* norm_w, float eps, cudaStream_t stream) {
   if (T <= 0) return 0;
   PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::embed_kernel<S>, dim3(T), dim3(256), 0, stream,
                                                static_cast<float*>(out), static_cast<const S*>(table), tokens,
-                                               mult, D, V));
+                                               mult, D, V, norm_w, eps));
   return pmm::launch_status();
 }
 
@@ -149,6 +209,28 @@ PMM_EXPORT int pmm_add_rmsnorm(void* h, const void* a, float sa, const void* b, 
     }
     pmm::launch_pdl(kern, dim3(R), dim3(threads), smem, stream, static_cast<float*>(h), static_cast<const S*>(a), sa,
                     static_cast<const S*>(b), sb, w, eps, static_cast<S*>(out), rows, D);
+  });
+  return pmm::launch_status();
+}
+
+// h [T, D] float or nullptr; a (and b or nullptr) [T, D] storage type; post_w, w float [D]; out [R, D] storage
+// type or nullptr; rows [R] or nullptr (then R = T).
+PMM_EXPORT int pmm_add_postnorm_rmsnorm(void* h, const void* a, float sa, const void* b, float sb, const float* post_w,
+                                        float post_eps, const float* w, float eps, void* out, const int* rows, int R,
+                                        int D, int dtype, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (D <= 0 || !a || !post_w || (rows && !out) || (!h && !out)) return PMM_ERR_BAD_ARGUMENT;
+  const size_t smem = static_cast<size_t>(D) * sizeof(float);
+  if (smem > 200 * 1024) return PMM_ERR_BAD_ARGUMENT;
+  const int threads = D >= 1024 ? 256 : 128;
+  PMM_DISPATCH_DTYPE(dtype, S, {
+    auto kern = pmm::add_postnorm_rmsnorm_kernel<S>;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    pmm::launch_pdl(kern, dim3(R), dim3(threads), smem, stream, static_cast<float*>(h), static_cast<const S*>(a), sa,
+                    static_cast<const S*>(b), sb, post_w, post_eps, w, eps, static_cast<S*>(out), rows, D);
   });
   return pmm::launch_status();
 }

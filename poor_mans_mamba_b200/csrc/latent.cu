@@ -11,9 +11,9 @@
 // of 16, zeros beyond) over ONE key/value head: key row [c | rot(r) | 0], value row [c | 0].
 //
 // latent_norm_store (a block per token): the query latent and the key/value latent are divided by
-// their root mean squares (float; x / sqrt(mean(x^2) + eps) * w), the rotated key part turns in
-// neighbouring pairs (2i, 2i+1) by the angle p * inv_freq[i], and the key and value rows go into their
-// cache page.  latent_query_rot (a block per token): the rotated part of every query head turns the
+// their root mean squares (float; x / sqrt(mean(x^2) + eps) * w; q_rank 0: the queries have no latent),
+// the rotated key part turns in neighbouring pairs (2i, 2i+1), or with ``half`` in pairs (i, i + rot_dims/2),
+// by the angle p * inv_freq[i], and the key and value rows go into their cache page.  latent_query_rot (a block per token): the rotated part of every query head turns the
 // same way and is written behind the head's latent part.  Positions, angles, sines, cosines and both
 // norms are float in both storage types.
 #include "common.cuh"
@@ -21,6 +21,21 @@
 namespace pmm {
 
 constexpr int kLatentMaxPairs = 128;  // rot_dims <= 256
+
+// Entry j (< rot_dims) of a rotated part turns together with its partner: neighbours (2i, 2i+1), or with
+// ``half`` entries (i, i + rot_dims/2); the angle is that of pair i.
+__device__ __forceinline__ void rot_partner(int j, int rot_dims, int half, int* partner, int* pair, bool* second) {
+  if (half) {
+    const int hd = rot_dims >> 1;
+    *second = j >= hd;
+    *pair = *second ? j - hd : j;
+    *partner = *second ? j - hd : j + hd;
+  } else {
+    *second = (j & 1) != 0;
+    *pair = j >> 1;
+    *partner = j ^ 1;
+  }
+}
 
 // x [T, >= q_rank] and kv [T, >= kv_rank + rot_dim]: rows of the stacked projection (strides ld_x, ld_kv).
 // cq [T, q_rank] contiguous.  pool [pages, planes, page_size, Dp]; planes 2: keys in plane 0, values in plane 1.
@@ -31,7 +46,7 @@ __global__ void __launch_bounds__(256)
                              const float* __restrict__ inv_freq, const int* __restrict__ positions,
                              const int* __restrict__ seq_of, const int* __restrict__ block_table, int max_blocks,
                              S* __restrict__ pool, int page_size, S* __restrict__ cq, int q_rank, int kv_rank,
-                             int rot_dim, int rot_dims, int Dp) {
+                             int rot_dim, int rot_dims, int Dp, int half) {
   __shared__ float red[32];
   __shared__ float sn_t[kLatentMaxPairs], cs_t[kLatentMaxPairs];
   pdl_launch_dependents();
@@ -45,7 +60,7 @@ __global__ void __launch_bounds__(256)
   float sq = 0.f, sk = 0.f;
   for (int i = threadIdx.x; i < q_rank; i += blockDim.x) { const float v = ldf(xr + i); sq += v * v; }
   for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) { const float v = ldf(kr + i); sk += v * v; }
-  const float inv_q = 1.f / sqrtf(block_sum(sq, red) / static_cast<float>(q_rank) + eps);
+  const float inv_q = q_rank > 0 ? 1.f / sqrtf(block_sum(sq, red) / static_cast<float>(q_rank) + eps) : 0.f;
   const float inv_k = 1.f / sqrtf(block_sum(sk, red) / static_cast<float>(kv_rank) + eps);  // (block_sum syncs: sn_t, cs_t are ready)
   for (int i = threadIdx.x; i < q_rank; i += blockDim.x) stf(cq + static_cast<size_t>(t) * q_rank + i, ldf(xr + i) * inv_q * q_w[i]);
   const int page = block_table[static_cast<size_t>(seq_of[t]) * max_blocks + pos / page_size];
@@ -60,9 +75,12 @@ __global__ void __launch_bounds__(256)
       const int j = i - kv_rank;
       const float a = ldf(kr + i);
       if (j < rot_dims) {
-        const float b = ldf(kr + kv_rank + (j ^ 1));
-        const float sn = sn_t[j >> 1], cs = cs_t[j >> 1];
-        kval = (j & 1) ? a * cs + b * sn : a * cs - b * sn;
+        int partner, pair;
+        bool second;
+        rot_partner(j, rot_dims, half, &partner, &pair, &second);
+        const float b = ldf(kr + kv_rank + partner);
+        const float sn = sn_t[pair], cs = cs_t[pair];
+        kval = second ? a * cs + b * sn : a * cs - b * sn;
       } else {
         kval = a;
       }
@@ -79,7 +97,7 @@ template <typename S>
 __global__ void __launch_bounds__(256)
     latent_query_rot_kernel(const S* __restrict__ q, long long ld_q, const float* __restrict__ inv_freq,
                             const int* __restrict__ positions, S* __restrict__ q_out, int H, int dim, int rot_dim,
-                            int rot_dims, int kv_rank, int Dp) {
+                            int rot_dims, int kv_rank, int Dp, int half) {
   __shared__ float sn_t[kLatentMaxPairs], cs_t[kLatentMaxPairs];
   pdl_launch_dependents();
   pdl_wait();
@@ -96,9 +114,12 @@ __global__ void __launch_bounds__(256)
       const S* part = qr + static_cast<size_t>(h) * (dim + rot_dim) + dim;
       const float a = ldf(part + j);
       if (j < rot_dims) {
-        const float b = ldf(part + (j ^ 1));
-        const float sn = sn_t[j >> 1], cs = cs_t[j >> 1];
-        val = (j & 1) ? a * cs + b * sn : a * cs - b * sn;
+        int partner, pair;
+        bool second;
+        rot_partner(j, rot_dims, half, &partner, &pair, &second);
+        const float b = ldf(part + partner);
+        const float sn = sn_t[pair], cs = cs_t[pair];
+        val = second ? a * cs + b * sn : a * cs - b * sn;
       } else {
         val = a;
       }
@@ -128,22 +149,22 @@ PMM_EXPORT int pmm_latent_norm_store(const void* x, long long ld_x, const void* 
                                      const float* kv_w, float eps, const float* inv_freq, const int* positions,
                                      const int* seq_of, const int* block_table, int max_blocks, void* pool,
                                      int page_size, void* cq, int T, int q_rank, int kv_rank, int rot_dim, int rot_dims,
-                                     int Dp, int dtype, cudaStream_t stream) {
+                                     int Dp, int half, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (q_rank <= 0 || kv_rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || rot_dims % 2 ||
+  if (q_rank < 0 || (q_rank > 0 && (!x || !q_w || !cq)) || kv_rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || rot_dims % 2 ||
       rot_dims > 2 * pmm::kLatentMaxPairs || (rot_dims > 0 && !inv_freq) || Dp < kv_rank + rot_dim || page_size <= 0)
     return PMM_ERR_BAD_ARGUMENT;
   PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::latent_norm_store_kernel<S>, dim3(T), dim3(256), 0, stream,
                                                static_cast<const S*>(x), ld_x, static_cast<const S*>(kv), ld_kv, q_w,
                                                kv_w, eps, inv_freq, positions, seq_of, block_table, max_blocks,
                                                static_cast<S*>(pool), page_size, static_cast<S*>(cq), q_rank, kv_rank,
-                                               rot_dim, rot_dims, Dp));
+                                               rot_dim, rot_dims, Dp, half));
   return pmm::launch_status();
 }
 
 PMM_EXPORT int pmm_latent_query_rot(const void* q, long long ld_q, const float* inv_freq, const int* positions,
                                     void* q_out, int T, int H, int dim, int rot_dim, int rot_dims, int kv_rank, int Dp,
-                                    int dtype, cudaStream_t stream) {
+                                    int half, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || dim <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || rot_dims % 2 ||
       rot_dims > 2 * pmm::kLatentMaxPairs || (rot_dims > 0 && !inv_freq) || Dp < kv_rank + rot_dim)
@@ -151,7 +172,7 @@ PMM_EXPORT int pmm_latent_query_rot(const void* q, long long ld_q, const float* 
   if (Dp == kv_rank) return 0;  // nothing behind the latent part
   PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::latent_query_rot_kernel<S>, dim3(T), dim3(256), 0, stream,
                                                static_cast<const S*>(q), ld_q, inv_freq, positions,
-                                               static_cast<S*>(q_out), H, dim, rot_dim, rot_dims, kv_rank, Dp));
+                                               static_cast<S*>(q_out), H, dim, rot_dim, rot_dims, kv_rank, Dp, half));
   return pmm::launch_status();
 }
 

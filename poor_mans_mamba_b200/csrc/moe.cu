@@ -77,7 +77,8 @@ __global__ void __launch_bounds__(kRouteWarps * 32)
   }
   __syncthreads();
   if (scored) {
-    // Scores s = sigmoid(z).  The choice runs on s + correction, among the experts of the `keep` groups (of `groups`
+    // Scores s = sigmoid(z) (scored == 2: s = softmax(z) over all experts, a group's score is its largest choice
+    // score, and the weights are the chosen s times scale, not divided by their sum).  The choice runs on s + correction, among the experts of the `keep` groups (of `groups`
     // equal groups of neighbours) whose two largest choice scores sum highest; every other expert's choice score is
     // -inf.  The weights are the chosen s over their sum (+ 1e-20), times scale.  The lower index wins a tie.
     float* extra = logits + TOK * E;
@@ -85,10 +86,29 @@ __global__ void __launch_bounds__(kRouteWarps * 32)
       float* z = logits + r * E;         // becomes the choice scores
       float* sc = extra + r * 2 * E;     // s
       float* gs = sc + E;                // group scores
-      for (int e = lane; e < E; e += 32) {
-        const float sv = 1.f / (1.f + expf(-z[e]));
-        sc[e] = sv;
-        z[e] = sv + (correction ? correction[e] : 0.f);
+      if (scored == 2) {
+        // scores: the softmax of z over all experts
+        float zmax = -INFINITY;
+        for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
+        zmax = warp_max(zmax);
+        float zsum = 0.f;
+        for (int e = lane; e < E; e += 32) {
+          const float ev = expf(z[e] - zmax);
+          sc[e] = ev;
+          zsum += ev;
+        }
+        const float zinv = 1.f / warp_sum(zsum);
+        for (int e = lane; e < E; e += 32) {
+          const float sv = sc[e] * zinv;
+          sc[e] = sv;
+          z[e] = sv + (correction ? correction[e] : 0.f);
+        }
+      } else {
+        for (int e = lane; e < E; e += 32) {
+          const float sv = 1.f / (1.f + expf(-z[e]));
+          sc[e] = sv;
+          z[e] = sv + (correction ? correction[e] : 0.f);
+        }
       }
       __syncwarp();
       if (groups > 1) {
@@ -99,7 +119,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32)
             const float v = z[e];
             if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
           }
-          gs[g] = per > 1 ? a + b : a;
+          gs[g] = (per > 1 && scored != 2) ? a + b : a;
         }
         __syncwarp();
         // the `keep` best groups are marked by +inf in gs; then the others' experts drop out
@@ -147,7 +167,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32)
         }
         __syncwarp();
       }
-      const float inv = scale / (denom + 1e-20f);
+      const float inv = scored == 2 ? scale : scale / (denom + 1e-20f);
       for (int j = lane; j < top; j += 32) weights[static_cast<size_t>(t0 + r) * top + j] *= inv;
     }
     return;
@@ -640,7 +660,8 @@ int launch_route(const void* x, long long ld_x, const float* w, const float* bia
 
 // scored == 0: the `top` largest logits, weights their softmax.  scored != 0: scores sigmoid(z); the choice runs on
 // score + correction (may be null) within the `keep` best of `groups` groups of neighbours; weights are the chosen
-// scores over their sum, times scale.
+// scores over their sum, times scale.  scored == 2: scores softmax(z) over all experts; groups are ranked by their
+// largest choice score; weights are the chosen scores times scale.
 PMM_EXPORT int pmm_moe_route(const void* x, long long ld_x, const float* w, const float* bias, int* ids, float* weights,
                              int T, int D, int E, int top, int scored, const float* correction, int groups, int keep,
                              float scale, const float* gate_w, float* gate_out, int dtype, cudaStream_t stream) {

@@ -20,14 +20,15 @@ constexpr int kRopeMaxPairs = 128;  // rot_dims <= 256
 // `sn`, `cs`: the token's sines and cosines per rotated pair (shared memory, made once a token).
 template <typename S>
 __device__ __forceinline__ float rotated(const S* __restrict__ head, const float* __restrict__ bias, int i, int rot_dims,
-                                         const float* __restrict__ sn_t, const float* __restrict__ cs_t, int half_layout) {
-  const float x = ldf(head + i) + (bias ? bias[i] : 0.f);
+                                         const float* __restrict__ sn_t, const float* __restrict__ cs_t, int half_layout,
+                                         const float* __restrict__ norm_w = nullptr, float inv = 1.f) {
+  const float x = (ldf(head + i) + (bias ? bias[i] : 0.f)) * (norm_w ? inv * norm_w[i] : 1.f);
   if (i >= rot_dims) return x;
   const int half = rot_dims >> 1;
   const bool second = half_layout ? i >= half : (i & 1);
   const int j = half_layout ? (second ? i - half : i + half) : (i ^ 1);
   const int f = half_layout ? (second ? i - half : i) : (i >> 1);
-  const float other = ldf(head + j) + (bias ? bias[j] : 0.f);
+  const float other = (ldf(head + j) + (bias ? bias[j] : 0.f)) * (norm_w ? inv * norm_w[j] : 1.f);
   const float sn = sn_t[f], cs = cs_t[f];
   return second ? x * cs + other * sn : x * cs - other * sn;
 }
@@ -40,14 +41,35 @@ __global__ void __launch_bounds__(256)
                             const int* __restrict__ block_table, int max_blocks, S* __restrict__ pool,
                             int page_size, S* __restrict__ q_out, int H, int G, int d, int dv, int Dp,
                             int rot_dims, int half_layout, const float* __restrict__ q_bias,
-                            const float* __restrict__ k_bias, const float* __restrict__ v_bias) {
+                            const float* __restrict__ k_bias, const float* __restrict__ v_bias,
+                            const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float norm_eps) {
   __shared__ float sn_t[kRopeMaxPairs], cs_t[kRopeMaxPairs];
+  __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const float fpos = static_cast<float>(pos);
   for (int f = threadIdx.x; f < rot_dims / 2; f += blockDim.x) sincosf(fpos * inv_freq[f], &sn_t[f], &cs_t[f]);
+  // q_norm_w / k_norm_w: all query rows of the token, and all its key rows, are divided by their root mean
+  // square (over the whole projection, before it is cut into heads) and multiplied by the weight, before rotation
+  float inv_q = 1.f, inv_k = 1.f;
+  if (q_norm_w) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
+      const float x = ldf(q + static_cast<long long>(t) * ld_q + i) + (q_bias ? q_bias[i] : 0.f);
+      ss += x * x;
+    }
+    inv_q = 1.f / sqrtf(block_sum(ss, red) / static_cast<float>(H * d) + norm_eps);
+  }
+  if (k_norm_w) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < G * d; i += blockDim.x) {
+      const float x = ldf(k + static_cast<long long>(t) * ld_k + i) + (k_bias ? k_bias[i] : 0.f);
+      ss += x * x;
+    }
+    inv_k = 1.f / sqrtf(block_sum(ss, red) / static_cast<float>(G * d) + norm_eps);
+  }
   __syncthreads();
   const int n_q = H * Dp, n_kv = G * Dp;
   const int page = block_table[static_cast<size_t>(seq_of[t]) * max_blocks + pos / page_size];
@@ -57,12 +79,12 @@ __global__ void __launch_bounds__(256)
     if (e < n_q) {
       const int h = e / Dp, i = e - h * Dp;
       const float val = i < d ? rotated(q + static_cast<long long>(t) * ld_q + h * d, q_bias ? q_bias + h * d : nullptr, i, rot_dims,
-                                        sn_t, cs_t, half_layout) : 0.f;
+                                        sn_t, cs_t, half_layout, q_norm_w ? q_norm_w + h * d : nullptr, inv_q) : 0.f;
       stf(q_out + static_cast<size_t>(t) * n_q + e, val);
     } else if (e < n_q + n_kv) {
       const int c = e - n_q, g = c / Dp, i = c - g * Dp;
       const float val = i < d ? rotated(k + static_cast<long long>(t) * ld_k + g * d, k_bias ? k_bias + g * d : nullptr, i, rot_dims,
-                                        sn_t, cs_t, half_layout) : 0.f;
+                                        sn_t, cs_t, half_layout, k_norm_w ? k_norm_w + g * d : nullptr, inv_k) : 0.f;
       stf(k_row + c, val);
     } else {
       const int c = e - n_q - n_kv, g = c / Dp, i = c - g * Dp;
@@ -75,12 +97,14 @@ __global__ void __launch_bounds__(256)
 
 // q [T, H*d], k [T, G*d], v [T, G*dv] rows of stride ld; inv_freq [rot_dims/2] floats (may be nullptr when
 // rot_dims is 0); pool [pages, 2, page_size, G*Dp]; q_out [T, H*Dp]; q_bias [H*d], k_bias [G*d], v_bias [G*dv]
-// floats or nullptr.
+// floats or nullptr; q_norm_w [H*d], k_norm_w [G*d] floats or nullptr: an RMS norm over the token's whole query
+// (key) projection before rotation, eps inside the root.  Values are never normed.
 PMM_EXPORT int pmm_rope_pairs_store(const void* q, long long ld_q, const void* k, long long ld_k, const void* v,
                                     long long ld_v, const float* inv_freq, const int* positions, const int* seq_of,
                                     const int* block_table, int max_blocks, void* pool, int page_size, void* q_out,
                                     int T, int H, int G, int d, int dv, int Dp, int rot_dims, int half_layout,
-                                    const float* q_bias, const float* k_bias, const float* v_bias, int dtype,
+                                    const float* q_bias, const float* k_bias, const float* v_bias,
+                                    const float* q_norm_w, const float* k_norm_w, float norm_eps, int dtype,
                                     cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || G <= 0 || d <= 0 || dv <= 0 || Dp < d || Dp < dv || rot_dims < 0 || rot_dims > d || rot_dims % 2 ||
@@ -91,6 +115,6 @@ PMM_EXPORT int pmm_rope_pairs_store(const void* q, long long ld_q, const void* k
                                                static_cast<const S*>(v), ld_v, inv_freq, positions, seq_of,
                                                block_table, max_blocks, static_cast<S*>(pool), page_size,
                                                static_cast<S*>(q_out), H, G, d, dv, Dp, rot_dims, half_layout, q_bias,
-                                               k_bias, v_bias));
+                                               k_bias, v_bias, q_norm_w, k_norm_w, norm_eps));
   return pmm::launch_status();
 }

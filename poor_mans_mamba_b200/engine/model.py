@@ -2,7 +2,7 @@
 order in which the layers run, final norm and output head.
 
 The forward pass is the same for every architecture:
-  h = multiplier * E[tokens]                       (float32 residual stream)
+  h = multiplier * E[tokens]                       (float32 residual stream; then the embedding's norm, if any)
   for (layer, cache_of) in order: layers[layer](h, cache of cache_of)
   logits = (norm(h)[wanted rows] @ W_head^T) * head_multiplier       (float32)
 (reference src/runtime/runner/falconh1_runner.cpp:129-228, which keeps the last row only).
@@ -50,6 +50,9 @@ class Model:
             self.reentry = build_part("stream_update", spec.reentry, hidden_size=spec.hidden_size)
         elif any(call.enters for call in spec.order):
             raise ValueError("the execution order re-enters the stream but the model has no reentry part")
+        self.embedding_norm = None
+        if spec.embedding_norm is not None:
+            self.embedding_norm = build_part("norm", spec.embedding_norm, width=spec.hidden_size)
         self.embedding: Optional[Tensor] = None
         self.head: Optional[Tensor] = None
         self.dtype: Optional[torch.dtype] = None
@@ -66,6 +69,8 @@ class Model:
             for part in layer.parts():
                 out.append((f"{layer.prefix}{part.name}", part))
         out.append((self.spec.final_norm.name, self.final_norm))
+        if self.embedding_norm is not None:
+            out.append((self.spec.embedding_norm.name, self.embedding_norm))
         if self.reentry is not None:
             out.append((self.spec.reentry.name, self.reentry))
         return out
@@ -104,6 +109,10 @@ class Model:
         for layer in self.layers:
             layer.finalize(dtype, self.device)
         self.final_norm.finalize(dtype, self.device)
+        if self.embedding_norm is not None:
+            self.embedding_norm.finalize(dtype, self.device)
+            if self.embedding_norm.rms_prologue() is None:
+                raise ValueError("the embedding's norm must be an RMS norm")
         if self.reentry is not None:
             self.reentry.finalize(dtype, self.device)
 
@@ -131,7 +140,11 @@ class Model:
         ws = ctx.workspace
         T, D = ctx.n_tokens, self.hidden_size
         h = ws.alloc((T, D), torch.float32)
-        K.embed(h, self.embedding, ctx.tokens, self.spec.embedding_multiplier)
+        if self.embedding_norm is not None:
+            norm_w, norm_eps = self.embedding_norm.rms_prologue()
+            K.embed(h, self.embedding, ctx.tokens, self.spec.embedding_multiplier, norm_w, norm_eps)
+        else:
+            K.embed(h, self.embedding, ctx.tokens, self.spec.embedding_multiplier)
         stream = ResidualStream(h, ctx, self._branch_buffers, lanes=self.spec.residual_lanes)
         if self.reentry is not None:
             stream.reentry = ws.alloc((T, 2 * D), ctx.dtype)

@@ -28,7 +28,9 @@ class KernelError(RuntimeError):
 
 
 _SIGNATURES = {
-    "pmm_embed": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_embed": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p],
+    "pmm_add_postnorm_rmsnorm": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_float, c_void_p, c_float,
+                                 c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_add_rmsnorm": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_float, c_void_p,
                         c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_scale_f32": [c_void_p, c_float, c_longlong, c_void_p],
@@ -60,14 +62,14 @@ _SIGNATURES = {
                      c_int, c_int, c_void_p],
     "pmm_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
-                            c_int, c_int, c_int, c_void_p, c_void_p],
+                            c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "pmm_hc_mix_norm": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_normed_sum": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int,
                        c_void_p],
     "pmm_rope_pairs_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+                             c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p],
     "pmm_delta_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
                        c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                        c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
@@ -112,6 +114,7 @@ _SIGNATURES = {
     "pmm_tc_gemm_act": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_float,
                         c_float, c_float, c_void_p, c_void_p],
     "pmm_silu_mul": [c_void_p, c_longlong, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    "pmm_gelu_tanh_mul": [c_void_p, c_longlong, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_add_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_add_tanh_norm": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -132,9 +135,9 @@ _SIGNATURES = {
                         c_float, c_float, c_float, c_void_p, c_void_p, c_void_p],
     "pmm_latent_norm_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_int, c_void_p],
+                              c_int, c_int, c_void_p],
     "pmm_latent_query_rot": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_int, c_void_p],
+                             c_int, c_int, c_int, c_void_p],
     "pmm_head_gate": [c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
                       c_void_p],
     "pmm_token_gated_update_fits": [c_int, c_int],
@@ -380,8 +383,11 @@ def linear_f32_out(x: Tensor, weight: Tensor, out: Tensor, scratch_low: Optional
 
 
 # ----------------------------------------------------------------------------- own kernels
-def embed(out: Tensor, table: Tensor, tokens: Tensor, mult: float) -> None:
-    _cuda(out, table, tokens)
+def embed(out: Tensor, table: Tensor, tokens: Tensor, mult: float, norm_weight: Optional[Tensor] = None,
+          eps: float = 0.0) -> None:
+    """out[t] = mult * table[tokens[t]] (float32); with ``norm_weight`` [D] the row is then divided by its root
+    mean square (eps inside the root) and multiplied by the weight, all in float."""
+    _cuda(out, table, tokens, norm_weight)
     T, D = out.shape
     if not (out.dtype == torch.float32 and out.is_contiguous()):
         raise KernelError("embed: out must be contiguous float32")
@@ -390,8 +396,44 @@ def embed(out: Tensor, table: Tensor, tokens: Tensor, mult: float) -> None:
     _i32(tokens, "embed: tokens")
     if not (tokens.numel() == T):
         raise KernelError("embed: one token per output row")
+    _f32vec(norm_weight, D, "embed: norm weight")
     _call("pmm_embed", out.data_ptr(), table.data_ptr(), tokens.data_ptr(), float(mult), T, D,
-          table.shape[0], _dt(table), _stream())
+          table.shape[0], _dt(table), _ptr(norm_weight), float(eps), _stream())
+
+
+def add_postnorm_rmsnorm(h: Optional[Tensor], branches: Sequence[Tuple[Tensor, float]], post_weight: Tensor, post_eps: float,
+                         weight: Optional[Tensor], eps: float, out: Optional[Tensor], rows: Optional[Tensor] = None) -> None:
+    """u = rmsnorm(s0*b0 + s1*b1) * post_weight;  h <- h + u (rows is None and h given);  out = rmsnorm(h + u) * weight
+    (``weight`` None: out = h + u, or u alone without h).  With ``rows`` h is left as it is and out[r] comes from row
+    rows[r].  One or two branches in the storage type; every statistic and sum is float."""
+    _cuda(h, post_weight, weight, out, rows)
+    if not (1 <= len(branches) <= 2):
+        raise KernelError("add_postnorm_rmsnorm: one or two branches")
+    T, D = branches[0][0].shape
+    if h is not None and not (h.dtype == torch.float32 and h.shape == (T, D) and h.is_contiguous()):
+        raise KernelError("add_postnorm_rmsnorm: the residual stream must be contiguous float32 [T, D]")
+    if not (D * 4 <= 200 * 1024):
+        raise KernelError(f"add_postnorm_rmsnorm: width {D} exceeds one block's shared memory")
+    ptrs: List[Optional[int]] = [None, None]
+    scales = [0.0, 0.0]
+    dtype = _dt(branches[0][0])
+    for i, (b, s) in enumerate(branches):
+        _cuda(b)
+        if not (b.shape == (T, D) and b.is_contiguous() and _dt(b) == dtype):
+            raise KernelError("add_postnorm_rmsnorm: branches must be contiguous [T, D] of one storage type")
+        ptrs[i], scales[i] = b.data_ptr(), float(s)
+    _f32vec(post_weight, D, "add_postnorm_rmsnorm: post weight")
+    _f32vec(weight, D, "add_postnorm_rmsnorm: weight")
+    R = T
+    if rows is not None:
+        _i32(rows, "add_postnorm_rmsnorm: rows")
+        R = rows.numel()
+    if out is not None and not (out.shape == (R, D) and out.is_contiguous() and _dt(out) == dtype):
+        raise KernelError("add_postnorm_rmsnorm: out must be contiguous [rows, D] of the branches' type")
+    if out is None and (h is None or rows is not None):
+        raise KernelError("add_postnorm_rmsnorm: nothing to write")
+    _call("pmm_add_postnorm_rmsnorm", _ptr(h), ptrs[0], scales[0], ptrs[1], scales[1], post_weight.data_ptr(),
+          float(post_eps), _ptr(weight), float(eps), _ptr(out), _ptr(rows), R, D, dtype, _stream())
 
 
 def add_rmsnorm(h: Tensor, branches: Sequence[Tuple[Tensor, float]], weight: Optional[Tensor],
@@ -870,8 +912,9 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
                     scratch: Optional[Tensor] = None, cu_seqlens: Optional[Tensor] = None,
                     new_lens: Optional[Sequence[int]] = None, use_tensor_cores: bool = True,
                     split_counter: Optional[Tensor] = None, tile_rows: Optional[int] = None,
-                    sink: Optional[Tensor] = None) -> None:
+                    sink: Optional[Tensor] = None, keep_first: int = 0) -> None:
     """Causal attention of every token over keys lo..pos of its request in the paged cache.
+    ``keep_first``: the request's first keep_first keys stay visible behind a window (at their true positions).
     ``sink`` (one float per query head): the softmax's denominator also holds exp(sink[h]), a score
     without key or value.
     With ``cu_seqlens`` and ``new_lens`` (tokens per sequence, host values) a bfloat16 cache of a
@@ -904,8 +947,10 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
         part_o = scratch.data_ptr()
         part_ml = part_o + 4 * T * n_q_heads * n_splits * head_dim
     _f32vec(sink, n_q_heads, "attention: sink")
+    if not (keep_first >= 0):
+        raise KernelError("attention: keep_first must not be negative")
     flash = (use_tensor_cores and q.dtype == torch.bfloat16 and cu_seqlens is not None and new_lens is not None
-             and flash_supported(n_q_heads, n_kv_heads, head_dim))
+             and flash_supported(n_q_heads, n_kv_heads, head_dim) and (keep_first == 0 or window == 0))
     if flash:
         _i32(cu_seqlens, "attention: cu_seqlens")
         group = n_q_heads // n_kv_heads
@@ -931,7 +976,7 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
         _call("pmm_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], positions.data_ptr(), seq_of.data_ptr(), out.data_ptr(), part_o, part_ml,
               float(softmax_scale), int(window), int(split_len), int(n_splits), pool.shape[2], T, n_q_heads,
-              n_kv_heads, head_dim, _dt(q), _ptr(sink), _stream())
+              n_kv_heads, head_dim, _dt(q), _ptr(sink), int(keep_first) if window > 0 else 0, _stream())
     if n_splits > 1:
         _call("pmm_flash_combine", part_o, part_ml, out.data_ptr(), T * n_q_heads, int(n_splits), head_dim,
               _dt(out), _stream())
@@ -1426,6 +1471,17 @@ def silu_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:
           _dt(gate_up), _stream())
 
 
+def gelu_tanh_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:
+    """out[t, f] = gelu_tanh(gate_up[t, f] * gate_mult) * gate_up[t, F + f], gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi)
+    (z + 0.044715 z^3)))."""
+    _cuda(gate_up, out)
+    ld = _rows_view(gate_up, "gelu_tanh_mul: gate_up")
+    T, F2 = gate_up.shape
+    if not (F2 % 2 == 0 and out.shape == (T, F2 // 2) and out.is_contiguous() and out.dtype == gate_up.dtype):
+        raise KernelError("gelu_tanh_mul: out must be contiguous [T, F] for gate_up [T, 2F]")
+    _call("pmm_gelu_tanh_mul", gate_up.data_ptr(), ld, float(gate_mult), out.data_ptr(), T, F2 // 2, _dt(gate_up), _stream())
+
+
 def sigmoid_gate(a: Tensor, g: Tensor, scale: float, out: Tensor, n_heads: int, stored_dim: int, dim: int) -> None:
     """out[t, h*dim + i] = scale * a[t, h*stored_dim + i] * sigmoid(g[t, h*dim + i]) for i < dim."""
     _cuda(a, g, out)
@@ -1462,33 +1518,44 @@ def latent_padded_dim(kv_rank: int, rot_dim: int) -> int:
 
 def latent_norm_store(q_lat: Tensor, kv_lat: Tensor, q_w: Tensor, kv_w: Tensor, eps: float, inv_freq: Optional[Tensor],
                       positions: Tensor, seq_of: Tensor, block_table: Tensor, pool: Tensor, cq: Tensor, kv_rank: int,
-                      rot_dim: int, rot_dims: int) -> None:
+                      rot_dim: int, rot_dims: int, half_layout: bool = False) -> None:
     """cq = rms(q_lat) * q_w; the cache rows of the step's tokens: key row [rms(kv_lat[:kv_rank]) * kv_w | the last
     rot_dim entries of kv_lat, of which the first rot_dims turn in neighbouring pairs | 0], value row [the normed
-    latent | 0], into ``pool`` [pages, 2, page_size, Dp].  Norms, angles, sines and cosines are float."""
+    latent | 0], into ``pool`` [pages, 2, page_size, Dp].  Norms, angles, sines and cosines are float.
+    ``half_layout``: entries (i, i + rot_dims/2) turn together instead of neighbours.  ``q_lat`` None (with q_w and
+    cq None): the queries have no latent, only the cache rows are made."""
     _cuda(q_lat, kv_lat, q_w, kv_w, inv_freq, positions, seq_of, block_table, pool, cq)
-    T, q_rank = q_lat.shape
-    if not (kv_lat.shape == (T, kv_rank + rot_dim) and q_lat.dtype == kv_lat.dtype == pool.dtype == cq.dtype
-            and q_lat.stride(1) == 1 and kv_lat.stride(1) == 1):
-        raise KernelError("latent_norm_store: q_lat [T, q_rank], kv_lat [T, kv_rank + rot_dim] of the pool's type")
-    if not (cq.shape == (T, q_rank) and cq.is_contiguous()):
-        raise KernelError("latent_norm_store: cq must be contiguous [T, q_rank]")
+    T = kv_lat.shape[0]
+    if q_lat is None:
+        if not (q_w is None and cq is None):
+            raise KernelError("latent_norm_store: no query latent means no q_w and no cq")
+        q_rank = 0
+        if not (kv_lat.shape == (T, kv_rank + rot_dim) and kv_lat.dtype == pool.dtype and kv_lat.stride(1) == 1):
+            raise KernelError("latent_norm_store: kv_lat [T, kv_rank + rot_dim] of the pool's type")
+    else:
+        q_rank = q_lat.shape[1]
+        if not (q_lat.shape[0] == T and kv_lat.shape == (T, kv_rank + rot_dim)
+                and q_lat.dtype == kv_lat.dtype == pool.dtype == cq.dtype and q_lat.stride(1) == 1 and kv_lat.stride(1) == 1):
+            raise KernelError("latent_norm_store: q_lat [T, q_rank], kv_lat [T, kv_rank + rot_dim] of the pool's type")
+        if not (cq.shape == (T, q_rank) and cq.is_contiguous()):
+            raise KernelError("latent_norm_store: cq must be contiguous [T, q_rank]")
     if not (pool.dim() == 4 and pool.shape[1] == 2 and pool.is_contiguous() and pool.shape[3] >= kv_rank + rot_dim):
         raise KernelError("latent_norm_store: pool must be contiguous [pages, 2, page_size, Dp >= kv_rank + rot_dim]")
-    _f32vec(q_w, q_rank, "latent_norm_store: q_w")
+    if q_lat is not None:
+        _f32vec(q_w, q_rank, "latent_norm_store: q_w")
     _f32vec(kv_w, kv_rank, "latent_norm_store: kv_w")
     _f32vec(inv_freq, rot_dims // 2, "latent_norm_store: inv_freq")
     _i32(positions, "latent_norm_store: positions")
     _i32(seq_of, "latent_norm_store: seq_of")
     _i32(block_table, "latent_norm_store: block_table")
-    _call("pmm_latent_norm_store", q_lat.data_ptr(), q_lat.stride(0), kv_lat.data_ptr(), kv_lat.stride(0), q_w.data_ptr(),
-          kv_w.data_ptr(), float(eps), _ptr(inv_freq), positions.data_ptr(), seq_of.data_ptr(), block_table.data_ptr(),
-          block_table.shape[1], pool.data_ptr(), pool.shape[2], cq.data_ptr(), T, q_rank, int(kv_rank), int(rot_dim),
-          int(rot_dims), pool.shape[3], _dt(q_lat), _stream())
+    _call("pmm_latent_norm_store", _ptr(q_lat), q_lat.stride(0) if q_lat is not None else 0, kv_lat.data_ptr(),
+          kv_lat.stride(0), _ptr(q_w), kv_w.data_ptr(), float(eps), _ptr(inv_freq), positions.data_ptr(), seq_of.data_ptr(),
+          block_table.data_ptr(), block_table.shape[1], pool.data_ptr(), pool.shape[2], _ptr(cq), T, q_rank, int(kv_rank),
+          int(rot_dim), int(rot_dims), pool.shape[3], int(bool(half_layout)), _dt(kv_lat), _stream())
 
 
 def latent_query_rot(q: Tensor, inv_freq: Optional[Tensor], positions: Tensor, q_out: Tensor, heads: int, dim: int,
-                     rot_dim: int, rot_dims: int, kv_rank: int, padded_dim: int) -> None:
+                     rot_dim: int, rot_dims: int, kv_rank: int, padded_dim: int, half_layout: bool = False) -> None:
     """q [T, heads * (dim + rot_dim)]: the rotated part of every head turns and goes to q_out[t, h, kv_rank ..
     kv_rank + rot_dim); the entries from there to padded_dim become zero; the first kv_rank stay as they are."""
     _cuda(q, inv_freq, positions, q_out)
@@ -1499,7 +1566,8 @@ def latent_query_rot(q: Tensor, inv_freq: Optional[Tensor], positions: Tensor, q
     _f32vec(inv_freq, rot_dims // 2, "latent_query_rot: inv_freq")
     _i32(positions, "latent_query_rot: positions")
     _call("pmm_latent_query_rot", q.data_ptr(), q.stride(0), _ptr(inv_freq), positions.data_ptr(), q_out.data_ptr(), T,
-          int(heads), int(dim), int(rot_dim), int(rot_dims), int(kv_rank), int(padded_dim), _dt(q), _stream())
+          int(heads), int(dim), int(rot_dim), int(rot_dims), int(kv_rank), int(padded_dim), int(bool(half_layout)), _dt(q),
+          _stream())
 
 
 def head_gate(a: Tensor, g: Optional[Tensor], scale: float, out: Tensor, heads: int, vdim: int) -> None:
@@ -1602,12 +1670,13 @@ def relu_squared(x: Tensor, out: Tensor) -> None:
 
 # ----------------------------------------------------------------------------- routed feed-forward
 def moe_route(x: Tensor, router_w: Tensor, router_b: Optional[Tensor], top: int, ids: Tensor, weights: Tensor,
-              scored: bool = False, correction: Optional[Tensor] = None, groups: int = 1, keep: int = 1,
+              scored = False, correction: Optional[Tensor] = None, groups: int = 1, keep: int = 1,
               scale: float = 1.0, gate_w: Optional[Tensor] = None, gate_out: Optional[Tensor] = None) -> None:
     """ids, weights [T, top] of z = x Wr^T + br (float arithmetic).  Plain: the ``top`` largest z and their softmax.
     ``scored``: s = sigmoid(z); the ``top`` largest of s + correction among the experts of the ``keep`` groups (of
     ``groups`` equal groups of neighbours) whose two largest s + correction sum highest; weights the chosen s over
-    their sum, times ``scale``.  ``gate_w`` [D] float32: gate_out[t] = sigmoid(x[t] . gate_w) as well."""
+    their sum, times ``scale``.  ``scored`` "softmax": s = softmax(z) over all experts, a group counts by its largest
+    s + correction, and the weights are the chosen s times ``scale`` (not divided by their sum).  ``gate_w`` [D] float32: gate_out[t] = sigmoid(x[t] . gate_w) as well."""
     _cuda(x, router_w, router_b, ids, weights, correction, gate_w, gate_out)
     T, D = x.shape
     E = router_w.shape[0]
@@ -1626,7 +1695,7 @@ def moe_route(x: Tensor, router_w: Tensor, router_b: Optional[Tensor], top: int,
         if not (gate_out is not None and gate_out.dtype == torch.float32 and gate_out.is_contiguous() and gate_out.numel() == T):
             raise KernelError("moe_route: gate_out must be contiguous float32 [T]")
     _call("pmm_moe_route", x.data_ptr(), _rows_view(x, "moe_route"), router_w.data_ptr(), _ptr(router_b), ids.data_ptr(),
-          weights.data_ptr(), T, D, E, int(top), int(bool(scored)), _ptr(correction), int(groups), int(keep), float(scale),
+          weights.data_ptr(), T, D, E, int(top), 2 if scored == "softmax" else int(bool(scored)), _ptr(correction), int(groups), int(keep), float(scale),
           _ptr(gate_w), _ptr(gate_out) if gate_w is not None else None, _dt(x), _stream())
 
 
@@ -1899,12 +1968,22 @@ def normed_sum(branches: Sequence[Tuple[Tensor, Tensor]], eps: float, scale: flo
 def rope_pairs_store(q: Tensor, k: Tensor, v: Tensor, inv_freq: Optional[Tensor], rot_dims: int, positions: Tensor,
                      seq_of: Tensor, block_table: Tensor, pool: Tensor, q_out: Tensor, n_heads: int,
                      n_kv_heads: int, dim: int, vdim: int, padded_dim: int, half_layout: bool = False,
-                     biases: Optional[Tuple[Tensor, Tensor, Tensor]] = None) -> None:
+                     biases: Optional[Tuple[Tensor, Tensor, Tensor]] = None,
+                     qk_norm: Optional[Tuple[Tensor, Tensor, float]] = None) -> None:
     """Rotates pairs among the first ``rot_dims`` entries of every query and key head (neighbours
     (2i, 2i+1), or with ``half_layout`` entries (i, i + rot_dims/2)), writes queries to q_out [T, H*Dp]
     and keys and values into their pages [pages, 2, page, G*Dp], every head padded with zeros to Dp =
-    ``padded_dim`` entries.  ``biases``: float vectors added to q, k and v as they are read."""
+    ``padded_dim`` entries.  ``biases``: float vectors added to q, k and v as they are read.  ``qk_norm`` (weight
+    [H*d], weight [G*d], eps): before rotation the token's whole query projection, and its whole key projection, is
+    divided by its root mean square and multiplied by the weight (float); values are left as they are."""
     _cuda(q, k, v, inv_freq, positions, seq_of, block_table, pool, q_out)
+    qn = kn = None
+    norm_eps = 0.0
+    if qk_norm is not None:
+        qn, kn, norm_eps = qk_norm
+        _cuda(qn, kn)
+        _f32vec(qn, n_heads * dim, "rope_pairs_store: q norm weight")
+        _f32vec(kn, n_kv_heads * dim, "rope_pairs_store: k norm weight")
     qb = kb = vb = None
     if biases is not None:
         qb, kb, vb = biases
@@ -1927,7 +2006,7 @@ def rope_pairs_store(q: Tensor, k: Tensor, v: Tensor, inv_freq: Optional[Tensor]
     _call("pmm_rope_pairs_store", q.data_ptr(), ld_q, k.data_ptr(), ld_k, v.data_ptr(), ld_v, _ptr(inv_freq),
           positions.data_ptr(), seq_of.data_ptr(), block_table.data_ptr(), block_table.shape[1], pool.data_ptr(),
           pool.shape[2], q_out.data_ptr(), T, n_heads, n_kv_heads, dim, vdim, padded_dim, int(rot_dims),
-          int(bool(half_layout)), _ptr(qb), _ptr(kb), _ptr(vb), _dt(q), _stream())
+          int(bool(half_layout)), _ptr(qb), _ptr(kb), _ptr(vb), _ptr(qn), _ptr(kn), float(norm_eps), _dt(q), _stream())
 
 
 # ----------------------------------------------------------------------------- matrix-state recurrences

@@ -11,4 +11,5 @@ from . import norm, rope, ffn, attention, mamba2, block  # noqa: F401  (registra
 from . import hyper, parallel, recurrent, window_attention  # noqa: F401  (registration)
 from . import gated_attention, moe  # noqa: F401  (registration)
 from . import latent_attention, stream_update  # noqa: F401  (registration)
+from . import conv_attention  # noqa: F401  (registration)
 from .block import ParallelPreNormBlock, ResidualStream, SharedNormParallelBlock, prenorm_layer, shared_norm_layer

@@ -48,7 +48,8 @@ class StateSpec:
 
     kind "paged": ``planes`` rows of ``width`` elements per token (keys and values: 2
     planes), kept in pages through a block table; ``window`` > 0 means only the last
-    ``window`` tokens are ever read, so older pages can be given back.
+    ``window`` tokens are ever read, so older pages can be given back; ``keep_first`` > 0: the first
+    ``keep_first`` tokens are read for ever as well, so the pages they lie in stay.
     kind "fixed": one tensor of ``shape`` per request, kept in a slot; zero for a new
     request.  dtype "compute" follows the engine's storage type, "float32" stays 32-bit.
     """
@@ -57,12 +58,14 @@ class StateSpec:
     planes: int = 0
     width: int = 0
     window: int = 0
+    keep_first: int = 0
     shape: Tuple[int, ...] = ()
     dtype: str = "compute"
 
     @staticmethod
-    def paged(name: str, planes: int, width: int, window: int = 0) -> "StateSpec":
-        return StateSpec(name=name, kind="paged", planes=planes, width=width, window=window)
+    def paged(name: str, planes: int, width: int, window: int = 0, keep_first: int = 0) -> "StateSpec":
+        return StateSpec(name=name, kind="paged", planes=planes, width=width, window=window,
+                         keep_first=keep_first if window > 0 else 0)
 
     @staticmethod
     def fixed(name: str, shape: Sequence[int], dtype: str = "float32") -> "StateSpec":
@@ -293,6 +296,9 @@ class ModelSpec:
     # With one, the embedding's output is kept for the whole step (in the storage type, as the right half
     # of ``ResidualStream.reentry`` [T, 2D]; the left half is the part's scratch).
     reentry: Optional[PartSpec] = None
+    # A norm applied to the embedding's output before the first layer (in float, inside the embedding launch;
+    # an RMS norm: one whose `rms_prologue` answers).
+    embedding_norm: Optional[PartSpec] = None
     # None: one residual stream [T, D].  n >= 1: the residual state is n lanes [n, T, D], all equal to
     # the embedding's output at the start and summed before the final norm (arrangements that mix
     # lanes, such as ``hyper_prenorm``, read and write them through the ResidualStream)

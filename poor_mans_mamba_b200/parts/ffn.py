@@ -1,6 +1,7 @@
-"""Dense SwiGLU feed-forward.
+"""Dense gated feed-forward (SwiGLU, or the same with the tanh form of GELU on the gate).
 
-g = (x Wg^T) * gate_multiplier; u = x Wu^T; out = (silu(g) * u) Wd^T; the down
+g = (x Wg^T) * gate_multiplier; u = x Wu^T; out = (act(g) * u) Wd^T with act = silu, or with
+``activation`` "gelu_tanh" act(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); the down
 multiplier is the part's ``out_scale`` and is applied where the branch joins the
 residual stream (reference src/ops/cpu_backend.cpp:494-531).  Gate and up weights are
 stacked into one [2F, D] matrix at load so the two projections are one product.
@@ -31,7 +32,11 @@ _TC_ENABLED = os.environ.get("PMM_TCGEN05_FFN", "1") == "1"
 
 class SwiGLU(FeedForward):
     def __init__(self, hidden_size: int, intermediate_size: int, gate_multiplier: float = 1.0,
-                 down_multiplier: float = 1.0, tensors=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+                 down_multiplier: float = 1.0, tensors=("gate_proj.weight", "up_proj.weight", "down_proj.weight"),
+                 activation: str = "silu"):
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError("activation is 'silu' or 'gelu_tanh'")
+        self.gelu = activation == "gelu_tanh"
         self.tensors = tuple(tensors)  # names of the gate, up and down matrices within the part
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
@@ -55,6 +60,12 @@ class SwiGLU(FeedForward):
         f = self.intermediate_size
         act = ctx.workspace.alloc((T, f), x.dtype)
         tiles = ((T + 255) // 256) * (f // 128)
+        if self.gelu:
+            gu = ctx.workspace.alloc((T, 2 * f), x.dtype)
+            streaming.linear(x, self.gate_up, gu, ctx)
+            K.gelu_tanh_mul(gu, self.gate_multiplier, act)
+            streaming.linear(act, self.down, out, ctx)
+            return
         if streaming.swiglu(x, self.gate_up, self.gate_multiplier, act, ctx):
             streaming.linear(act, self.down, out, ctx)  # a step of few tokens: both products stream their weights
             return
@@ -69,7 +80,7 @@ class SwiGLU(FeedForward):
     def forward_few_tokens(self, h: Tensor, norm, ctx) -> bool:
         """h += down_multiplier * (silu(g) * u) Wd^T with [g | u] = norm(h) [Wg; Wu]^T in two
         weight-streaming launches."""
-        if not streaming.eligible(ctx, self.hidden_size):
+        if self.gelu or not streaming.eligible(ctx, self.hidden_size):
             return False
         act = ctx.workspace.alloc((h.shape[0], self.intermediate_size), ctx.dtype)
         streaming.normed_swiglu(h, norm, self.gate_up, self.gate_multiplier, act, ctx)

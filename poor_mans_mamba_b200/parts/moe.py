@@ -1,7 +1,10 @@
 """Routed feed-forward: a mixture of small gated experts, optionally beside a shared one.
 
     z = Wr x + br (float arithmetic); a token's ``top`` experts are those with the largest z, their
-    weights p the softmax over the chosen z only;
+    weights p the softmax over the chosen z only (``router`` "softmax_all": scores s = softmax(z) over ALL
+    experts; only experts of the ``keep`` best of ``groups`` equal groups of neighbours can be chosen, a group
+    counting by its largest score; the ``top`` largest s are chosen and the weights are those s themselves,
+    not divided by their sum);
     expert e:  g = min(Wg_e x, limit), u = clamp(Wu_e x, -limit, limit),
                y_e = Wd_e [ g * sigmoid(act_alpha * g) * (u + act_shift) ];
     out = sum over the chosen e of p_e y_e  (+ the shared expert's output, same form with its own
@@ -41,11 +44,19 @@ _TC_MOE = os.environ.get("PMM_TCGEN05_MOE", "1") == "1"
 class RoutedGLU(FeedForward):
     def __init__(self, hidden_size: int, experts: int, top: int, expert_ff: int, expert_limit: float,
                  shared_ff: int = 0, shared_limit: float = 0.0, act_alpha: float = 1.702, act_shift: float = 1.0,
-                 router_bias: bool = True, out_multiplier: float = 1.0):
+                 router_bias: bool = True, out_multiplier: float = 1.0, router: str = "top_softmax", groups: int = 1,
+                 keep: int = 1):
         if not 1 <= top <= experts:
             raise ValueError("top must be between 1 and the number of experts")
         if expert_ff <= 0 or shared_ff < 0:
             raise ValueError("expert widths must be positive")
+        if router not in ("top_softmax", "softmax_all"):
+            raise ValueError("router is 'top_softmax' or 'softmax_all'")
+        if groups < 1 or experts % groups or not 1 <= keep <= groups or top > keep * (experts // groups):
+            raise ValueError("groups must divide the experts, keep <= groups, top <= keep * experts / groups")
+        if router == "top_softmax" and groups != 1:
+            raise ValueError("groups of experts need the 'softmax_all' router")
+        self.softmax_all, self.groups, self.keep = router == "softmax_all", int(groups), int(keep)
         self.hidden_size = int(hidden_size)
         self.experts, self.top, self.expert_ff = int(experts), int(top), int(expert_ff)
         self.expert_limit, self.shared_ff, self.shared_limit = float(expert_limit), int(shared_ff), float(shared_limit)
@@ -101,7 +112,11 @@ class RoutedGLU(FeedForward):
         A = T * top
         ids = ws.alloc((T, top), torch.int32)
         weights = ws.alloc((T, top), torch.float32)
-        K.moe_route(x, self.router_w, self.router_b, top, ids, weights)
+        if self.softmax_all:
+            K.moe_route(x, self.router_w, self.router_b, top, ids, weights, scored="softmax", groups=self.groups,
+                        keep=self.keep)
+        else:
+            K.moe_route(x, self.router_w, self.router_b, top, ids, weights)
         offsets = ws.alloc((E + 1,), torch.int32)
         tile_start = ws.alloc((E + 1,), torch.int32)
         perm = ws.alloc((A,), torch.int32)

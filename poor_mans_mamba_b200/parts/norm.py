@@ -2,7 +2,9 @@
 
 y = x * (1/sqrt(mean(x^2) + eps)) * w; eps inside the root, the weight multiplies after
 normalisation (reference src/ops/cpu/rms_norm.cpp:11-16).  Statistics are float32.  A weight
-stored around zero (y = ... * (1 + w)) is the same norm with ``offset`` 1.
+stored around zero (y = ... * (1 + w)) is the same norm with ``offset`` 1.  The RMS norm also serves as
+the *post* norm of a sublayer's result, x <- x + rms(result) * w: the launch that norms the next
+sublayer's input does both (`folds_post`).
 """
 from __future__ import annotations
 
@@ -47,14 +49,29 @@ class RMSNorm(Norm):
     def rms_prologue(self):
         return self.weight, self.eps
 
-    def forward(self, h: Tensor, pending, out: Tensor, rows: Optional[Tensor], ctx) -> None:
+    def folds_post(self, post: Norm) -> bool:
+        return isinstance(post, RMSNorm)
+
+    def forward(self, h: Tensor, pending, out: Tensor, rows: Optional[Tensor], ctx, post: Optional[Norm] = None) -> None:
         items = list(pending)
+        if post is not None and items:
+            # a sublayer's result, normed once more before it joins: x <- x + post(sum), out = norm(x), one launch
+            if not isinstance(post, RMSNorm) or len(items) > 2:
+                raise ValueError("the RMS norm folds a post norm of its own kind over at most two branches")
+            K.add_postnorm_rmsnorm(h, items, post.weight, post.eps, self.weight, self.eps, out, rows)
+            return
         while len(items) > 2:  # more than two branches: fold the surplus first
             if rows is not None:
                 raise ValueError("row-selected norm takes at most two pending branches")
             K.add_rmsnorm(h, items[:2], None, 0.0, None)
             items = items[2:]
         K.add_rmsnorm(h, items, self.weight, self.eps, out, rows)
+
+    def apply(self, pending, out: Tensor, ctx) -> None:
+        K.add_postnorm_rmsnorm(None, list(pending), self.weight, self.eps, None, 0.0, out)
+
+    def fold(self, h: Tensor, pending, ctx) -> None:
+        K.add_postnorm_rmsnorm(h, list(pending), self.weight, self.eps, None, 0.0, None)
 
 
 class TanhNorm(Norm):

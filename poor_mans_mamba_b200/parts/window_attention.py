@@ -34,8 +34,10 @@ _TC_FROM_TOKENS = 256   # shorter steps stay on the mma.sync kernel (few 128-row
 class PagedSoftmaxAttention(_StackedInput):
     """What the softmax-attention mixers over padded heads share: the tickets of the key splits and the
     choice of the attention kernel for a step (`_attend`).  A subclass sets ``heads``, ``kv_heads``,
-    ``padded_dim``, ``window``, ``scale`` and, where it has one, ``sink``."""
+    ``padded_dim``, ``window``, ``scale`` and, where it has them, ``sink`` and ``keep_first`` (the
+    request's first keys that stay visible behind the window)."""
     sink: Optional[Tensor] = None
+    keep_first: int = 0
 
     def _make_split_counter(self, device: torch.device) -> None:
         # tickets of the key splits (zero between steps): the last block of a tile merges them
@@ -52,6 +54,9 @@ class PagedSoftmaxAttention(_StackedInput):
         counter = self._split_counter
         # (the tensor-core kernels take the row maximum before the scale is applied: positive scales only)
         bf16 = q_rot.dtype == torch.bfloat16 and counter is not None and self.scale > 0.0
+        keep = self.keep_first if self.window > 0 else 0
+        if keep > 0:
+            bf16 = False  # kept first keys behind a window: the float kernel walks the two key ranges
 
         def scratch_for(n_splits):
             return ws.alloc((K.attention_scratch_floats(T, H, Dp, n_splits),), torch.float32) if n_splits > 1 else None
@@ -77,7 +82,8 @@ class PagedSoftmaxAttention(_StackedInput):
         n_splits, split_len = plan_key_splits(H, G, Dp, self.window, ctx.new_lens, ctx.kv_len_bound, q_rot.dtype)
         K.paged_attention(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.seq_of, attn, H, G, Dp, self.scale,
                           window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch_for(n_splits),
-                          cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens, split_counter=counter, sink=self.sink)
+                          cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens, split_counter=counter, sink=self.sink,
+                          keep_first=keep)
 
 
 class WindowSinkAttention(PagedSoftmaxAttention):
