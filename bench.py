@@ -23,7 +23,8 @@ L2 flush is needed between timed iterations.
 `--workload compare` is a measurement beside the benchmark (its own JSON line): a Boketar model (or, with
 `--design tafesun`, a Tafesun model) and a Falcon-H1 model of equal width, feed-forward size, layer count and
 vocabulary, one prompt step and decode steps of each with the L2 flushed before every timed step, and every
-kernel's device time.  `--design gikovik` measures a Gikovik model beside the Tafesun model (the closest one:
+kernel's device time.  `--design sorovik` measures a Sorovik model beside the Tafesun and the Gikovik models.
+`--design gikovik` measures a Gikovik model beside the Tafesun model (the closest one:
 paged softmax attention and routed experts) in the same way.
 """
 from __future__ import annotations
@@ -547,6 +548,33 @@ def gikovik_config(falcon, mixer_sizes, ff_sizes, layers):
             "layers": out}
 
 
+# `--workload compare --design sorovik`: a Sorovik model beside the Tafesun and the Gikovik models above (equal
+# width, layers, vocabulary, experts, experts a token and expert widths).  Of every four layers the first and the
+# third are latent layers with rows of their own (96 latent entries beside 32 rotated ones: a cache row of 128), the
+# second is an attention layer with Falcon-H1's head counts and head size, and the fourth reads the third's rows.
+# Windows of 1,024 tokens; the attention layers keep the first four.
+def sorovik_config(falcon, mixer_sizes, ff_sizes, layers):
+    experts, top, expert_ff, _ = ff_sizes
+    heads, dim, vdim, _ = mixer_sizes
+    hd = falcon["head_dim"]
+    lat = {"heads": heads, "dim": dim, "rot_dim": 32, "vdim": vdim, "kv_rank": 96, "scale": (dim + 32) ** -0.5,
+           "rot": {"dims": 32, "base": 1e6}, "mask": {"size": 1024}}
+    att = {"heads": falcon["num_attention_heads"], "kv_heads": falcon["num_key_value_heads"], "dim": hd, "vdim": hd,
+           "conv": 3, "scale": hd ** -0.5, "rot": {"dims": hd // 2, "base": 5e4}, "mask": {"size": 1024, "keep_first": 4}}
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": expert_ff}}
+    out = []
+    for i in range(layers):
+        if i % 4 == 1:
+            out.append({"type": "attention", "mixer": att, "mlp": mlp})
+        elif i % 4 == 3:
+            out.append({"type": "latent_attention", "mixer": dict(lat, kv_from=i - 1), "mlp": mlp})
+        else:
+            out.append({"type": "latent_attention", "mixer": lat, "mlp": mlp})
+    return {"architecture": "Sorovik", "vocab": falcon["vocab_size"], "width": falcon["hidden_size"], "norm": {"eps": 1e-6},
+            "layers": out}
+
+
 def compare_workload(args, peaks) -> int:
     import torch
 
@@ -561,7 +589,13 @@ def compare_workload(args, peaks) -> int:
     falcon.update(falcon_keys)
     falcon["num_hidden_layers"] = layers
     vocab = falcon["vocab_size"]
-    if args.design == "gikovik":
+    if args.design == "sorovik":
+        configs = {"sorovik": sorovik_config(falcon, GIKOVIK_MIXER[args.sizes], TAFESUN_FF[args.sizes], layers),
+                   "tafesun": tafesun_config(falcon, TAFESUN_FF[args.sizes], layers),
+                   "gikovik": gikovik_config(falcon, GIKOVIK_MIXER[args.sizes], TAFESUN_FF[args.sizes], layers)}
+        design_sizes = {"routed_ff": dict(zip(("experts", "top", "expert_ff", "shared_ff"), TAFESUN_FF[args.sizes])),
+                        "latent_mixer": dict(zip(("heads", "dim", "vdim", "q_rank"), GIKOVIK_MIXER[args.sizes]))}
+    elif args.design == "gikovik":
         configs = {"gikovik": gikovik_config(falcon, GIKOVIK_MIXER[args.sizes], TAFESUN_FF[args.sizes], layers),
                    "tafesun": tafesun_config(falcon, TAFESUN_FF[args.sizes], layers)}
         design_sizes = {"routed_ff": dict(zip(("experts", "top", "expert_ff", "shared_ff"), TAFESUN_FF[args.sizes])),
@@ -690,8 +724,9 @@ def main() -> int:
                          "count (--layers, default 4) and vocabulary at --sizes 0.5b or 7b: one prompt step of "
                          "--prompt-tokens and decode steps of --batch requests at --context, device-timed with the "
                          "L2 flushed, and the device time of every kernel of one step of each")
-    ap.add_argument("--design", default="boketar", choices=["boketar", "tafesun", "gikovik"],
-                    help="--workload compare: the model that is measured beside Falcon-H1 (gikovik: beside Tafesun)")
+    ap.add_argument("--design", default="boketar", choices=["boketar", "tafesun", "gikovik", "sorovik"],
+                    help="--workload compare: the model that is measured beside Falcon-H1 (gikovik: beside Tafesun; "
+                         "sorovik: beside Tafesun and Gikovik)")
     ap.add_argument("--no-check", dest="check", action="store_false",
                     help="skip the comparison with the plain implementation that runs before the timing: the first "
                          "two layers of the run's model, in the run's dtype, on the benchmark's schedule (a "

@@ -20,7 +20,7 @@
 namespace pmm {
 
 constexpr int kAttnWarps = 4;
-constexpr int kAttnMaxAcc = 8;  // head_dim <= 256
+constexpr int kAttnMaxHead = 512;  // head sizes up to 256 keep 8 sums a lane, larger ones (rows of latents) 16
 
 __device__ __forceinline__ float dot_row(const float* __restrict__ qw, const float* __restrict__ kr, int Dh) {
   float dot = 0.f;
@@ -50,7 +50,7 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ qw, const __n
   return dot;
 }
 
-template <typename S>
+template <typename S, int kAttnMaxAcc>
 __global__ void __launch_bounds__(kAttnWarps * 32)
     paged_attention_kernel(const S* __restrict__ q, const S* __restrict__ pool,
                            const int* __restrict__ block_table, int max_blocks,
@@ -160,7 +160,7 @@ PMM_EXPORT int pmm_paged_attention(const void* q, const void* pool, const int* b
                                    int Hkv, int Dh, int dtype, const float* sink, int keep_first,
                                    cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (Dh <= 0 || Dh % 16 || Dh > 32 * pmm::kAttnMaxAcc) return PMM_ERR_BAD_ARGUMENT;
+  if (Dh <= 0 || Dh % 16 || Dh > pmm::kAttnMaxHead) return PMM_ERR_BAD_ARGUMENT;
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || page_size <= 0 || n_splits < 1 || n_splits > 65535)
     return PMM_ERR_BAD_ARGUMENT;
   if (n_splits > 1 && (!part_o || !part_ml || split_len <= 0)) return PMM_ERR_BAD_ARGUMENT;
@@ -171,7 +171,8 @@ PMM_EXPORT int pmm_paged_attention(const void* q, const void* pool, const int* b
   dim3 grid(T, head_blocks, n_splits);
   const size_t smem = static_cast<size_t>(pmm::kAttnWarps) * Dh * sizeof(float);
   PMM_DISPATCH_DTYPE(dtype, S, {
-    pmm::paged_attention_kernel<S><<<grid, pmm::kAttnWarps * 32, smem, stream>>>(
+    auto kern = Dh <= 256 ? pmm::paged_attention_kernel<S, 8> : pmm::paged_attention_kernel<S, 16>;
+    kern<<<grid, pmm::kAttnWarps * 32, smem, stream>>>(
         static_cast<const S*>(q), static_cast<const S*>(pool), block_table, max_blocks, positions,
         seq_of, static_cast<S*>(out), part_o, part_ml, scale, window, split_len, n_splits,
         page_size, Hq, Hkv, Dh, sink, keep_first);

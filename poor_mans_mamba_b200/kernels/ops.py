@@ -815,9 +815,14 @@ def gated_norm(y: Tensor, z_raw: Tensor, z_scale: float, z_bias: Optional[Tensor
           int(y.dtype == torch.float32 and out.dtype != torch.float32), int(gate == "sigmoid"), _stream())
 
 
-def check_head_dim(head_dim: int) -> None:
-    if not (head_dim % 16 == 0 and 16 <= head_dim <= 256):
-        raise KernelError(f"attention kernels take head sizes 16..256 in steps of 16, got {head_dim}")
+def check_head_dim(head_dim: int, limit: int = 256) -> None:
+    """Head sizes the attention kernels take: up to 256 on the tensor cores; the float kernel, which every
+    other size falls to, up to ``FLOAT_ATTENTION_MAX_HEAD`` (the rows of wide latents)."""
+    if not (head_dim % 16 == 0 and 16 <= head_dim <= limit):
+        raise KernelError(f"attention kernels take head sizes 16..{limit} in steps of 16, got {head_dim}")
+
+
+FLOAT_ATTENTION_MAX_HEAD = 512
 
 
 def qkv_rope_store(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], q_scale: float, k_scale: float,
@@ -923,7 +928,7 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
     tensor-core kernel merge its key splits itself instead of in a second launch.  ``tile_rows``
     (rows of (token, query head of a group) per block: 16, 64 or 128) defaults to flash_tile_rows."""
     _cuda(q, pool, block_table, positions, seq_of, out, scratch, cu_seqlens)
-    check_head_dim(head_dim)
+    check_head_dim(head_dim, FLOAT_ATTENTION_MAX_HEAD)
     T = q.shape[0]
     if not (q.is_contiguous() and out.is_contiguous() and q.shape == (T, n_q_heads * head_dim)
             and out.shape == q.shape and q.dtype == out.dtype == pool.dtype):

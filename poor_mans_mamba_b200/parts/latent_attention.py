@@ -73,7 +73,7 @@ class LatentAttention(PagedSoftmaxAttention):
         self.has_sink, self.has_gate = bool(sink), bool(gate)
         self.out_scale = float(out_multiplier)
         self.padded_dim = K.latent_padded_dim(self.kv_rank, self.rot_dim)
-        K.check_head_dim(self.padded_dim)
+        K.check_head_dim(self.padded_dim, K.FLOAT_ATTENTION_MAX_HEAD)
         self.q_head = self.dim + self.rot_dim
         self.kv_lat = self.kv_rank + self.rot_dim
         self.o_dim = self.heads * self.vdim

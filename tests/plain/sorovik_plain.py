@@ -136,8 +136,9 @@ def conv_attention(x: Tensor, W: Dict[str, Tensor], pre: str, m: dict, eps: floa
     v = k.reshape(T, G, d)
     q = rms_norm(q, W[pre + "q.norm"], eps).reshape(T, H, d)
     k = rms_norm(k, W[pre + "k.norm"], eps).reshape(T, G, d)
-    q = rotate_halves(q, positions, m["rot"]["dims"], m["rot"]["base"])
-    k = rotate_halves(k, positions, m["rot"]["dims"], m["rot"]["base"])
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
+    q = rotate_halves(q, positions, rot["dims"], rot["base"])
+    k = rotate_halves(k, positions, rot["dims"], rot["base"])
     rep = H // G
     k_h = k.repeat_interleave(rep, dim=1)
     v_h = v.repeat_interleave(rep, dim=1)
