@@ -150,7 +150,100 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   }
 }
 
+// The first keys of a request that stay visible behind a sliding window, merged into a windowed result.
+// `out` [T, Hq*Dh] holds every row's normalised result over its window keys (and sink), `lse` [T, Hq, 2] that
+// result's maximum score (natural-log units, scale applied) and sum of exponentials.  A warp per (token, query
+// head) walks the keys [0, min(keep_first, pos - window + 1)), the kept ones its window has left behind, with
+// an online softmax, and rewrites the row as the softmax over both sets:
+//   M = max(m, m_k);  out <- (out * l e^(m - M) + sum_k e^(s_k - M) v_k) / (l e^(m - M) + sum_k e^(s_k - M)).
+template <typename S, int kAttnMaxAcc>
+__global__ void __launch_bounds__(kAttnWarps * 32)
+    kept_first_merge_kernel(const S* __restrict__ q, const S* __restrict__ pool, const int* __restrict__ block_table,
+                            int max_blocks, const int* __restrict__ positions, const int* __restrict__ seq_of,
+                            S* __restrict__ out, const float* __restrict__ lse, float scale, int window, int keep_first,
+                            int page_size, int Hq, int Hkv, int Dh) {
+  extern __shared__ float qs[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int hq = blockIdx.y * kAttnWarps + warp;
+  if (hq >= Hq) return;  // only warp-level synchronisation below
+  const int pos = positions[t];
+  const int n_keys = min(keep_first, pos - window + 1);  // kept keys that the window no longer holds
+  if (n_keys <= 0) return;
+  const int hk = hq / (Hq / Hkv);
+  const int* bt = block_table + static_cast<size_t>(seq_of[t]) * max_blocks;
+  const int kv_dim = Hkv * Dh;
+  const long long v_plane = static_cast<long long>(page_size) * kv_dim;
+  float* qw = qs + warp * Dh;
+  const size_t q_off = (static_cast<size_t>(t) * Hq + hq) * Dh;
+  for (int d = lane; d < Dh; d += 32) qw[d] = ldf(q + q_off + d);
+  __syncwarp();
+  float m = -CUDART_INF_F, l = 0.f;
+  float acc[kAttnMaxAcc];
+#pragma unroll
+  for (int i = 0; i < kAttnMaxAcc; ++i) acc[i] = 0.f;
+  for (int base = 0; base < n_keys; base += 32) {
+    const int key = base + lane;
+    const bool valid = key < n_keys;
+    long long koff = 0;
+    float sc = -CUDART_INF_F;
+    if (valid) {
+      const int page = bt[key / page_size];
+      koff = (static_cast<long long>(page) * 2 * page_size + key % page_size) * kv_dim + hk * Dh;
+      sc = dot_row(qw, pool + koff, Dh) * scale;
+    }
+    const float m_new = fmaxf(m, warp_max(sc));
+    const float p = valid ? expf(sc - m_new) : 0.f;
+    const float corr = expf(m - m_new);
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < kAttnMaxAcc; ++i) acc[i] *= corr;
+    const int n_valid = min(32, n_keys - base);
+    for (int j = 0; j < n_valid; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      const long long voff = __shfl_sync(0xffffffffu, koff, j) + v_plane;
+#pragma unroll
+      for (int i = 0; i < kAttnMaxAcc; ++i) {
+        const int d = lane + 32 * i;
+        if (d < Dh) acc[i] += pj * ldf(pool + voff + d);
+      }
+    }
+    m = m_new;
+  }
+  const float m_w = lse[(static_cast<size_t>(t) * Hq + hq) * 2], l_w = lse[(static_cast<size_t>(t) * Hq + hq) * 2 + 1];
+  const float big = fmaxf(m, l_w > 0.f ? m_w : -CUDART_INF_F);
+  const float a = l_w > 0.f ? l_w * expf(m_w - big) : 0.f;  // weight of the windowed result
+  const float b = expf(m - big);
+  const float inv = 1.f / (a + b * l);
+#pragma unroll
+  for (int i = 0; i < kAttnMaxAcc; ++i) {
+    const int d = lane + 32 * i;
+    if (d < Dh) stf(out + q_off + d, (ldf(out + q_off + d) * a + acc[i] * b) * inv);
+  }
+}
+
 }  // namespace pmm
+
+PMM_EXPORT int pmm_kept_first_merge(const void* q, const void* pool, const int* block_table, int max_blocks,
+                                    const int* positions, const int* seq_of, void* out, const float* lse, float scale,
+                                    int window, int keep_first, int page_size, int T, int Hq, int Hkv, int Dh, int dtype,
+                                    cudaStream_t stream) {
+  if (T <= 0 || keep_first <= 0 || window <= 0) return 0;
+  if (Dh <= 0 || Dh % 16 || Dh > pmm::kAttnMaxHead || Hq <= 0 || Hkv <= 0 || Hq % Hkv || page_size <= 0 || !lse)
+    return PMM_ERR_BAD_ARGUMENT;
+  const int head_blocks = (Hq + pmm::kAttnWarps - 1) / pmm::kAttnWarps;
+  if (head_blocks > 65535) return PMM_ERR_BAD_ARGUMENT;
+  const size_t smem = static_cast<size_t>(pmm::kAttnWarps) * Dh * sizeof(float);
+  PMM_DISPATCH_DTYPE(dtype, S, {
+    auto kern = Dh <= 256 ? pmm::kept_first_merge_kernel<S, 8> : pmm::kept_first_merge_kernel<S, 16>;
+    pmm::launch_pdl(kern, dim3(T, head_blocks), dim3(pmm::kAttnWarps * 32), smem, stream, static_cast<const S*>(q),
+                    static_cast<const S*>(pool), block_table, max_blocks, positions, seq_of, static_cast<S*>(out), lse,
+                    scale, window, keep_first, page_size, Hq, Hkv, Dh);
+  });
+  return pmm::launch_status();
+}
 
 // part_o needs T*Hq*n_splits*Dh floats and part_ml T*Hq*n_splits*2 floats when n_splits > 1.
 PMM_EXPORT int pmm_paged_attention(const void* q, const void* pool, const int* block_table,

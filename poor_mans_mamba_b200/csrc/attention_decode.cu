@@ -74,6 +74,8 @@ struct DecodeAttnArgs {
   int* status;
   int clustered;          // the key splits of a (sequence, head) are one cluster (gridDim.z blocks)
   const float* sink;      // [Hq] or nullptr: exp(sink[h]) joins every row's softmax denominator once
+  float* lse;             // [n_seq, Hq, 2] or nullptr: with one key split, every row's (maximum in natural-log
+                          // units, sum of exponentials) beside its normalised result, for a later merge
 };
 
 // Address of a shared-memory location of this block in block `rank` of the cluster.
@@ -508,6 +510,8 @@ __global__ void __launch_bounds__(kDaThreads)
     if (n_splits == 1) {
       const float l = s_L[r];
       a.out[(static_cast<size_t>(seq) * a.Hq + hq) * DH + d] = __float2bfloat16_rn(l > 0.f ? sum / l : 0.f);
+      if (a.lse != nullptr && d == 0)
+        *reinterpret_cast<float2*>(a.lse + (static_cast<size_t>(seq) * a.Hq + hq) * 2) = make_float2(s_M[r] * kLn2, l);
     } else {
       const size_t pi = (static_cast<size_t>(seq) * a.Hq + hq) * n_splits + z;
       a.part_o[pi * DH + d] = sum;
@@ -641,8 +645,9 @@ PMM_EXPORT int pmm_decode_attention_tma(const void* q_src, long long ldq, const 
                                         int max_blocks, const int* positions, void* out, float* part_o, float* part_ml,
                                         float scale, int window, int split_len, int n_splits, int page_size, int n_seq,
                                         int Hq, int Hkv, int Dh, int* split_counter, int* status, const float* sink,
-                                        cudaStream_t stream) {
+                                        float* lse, cudaStream_t stream) {
   if (n_seq <= 0) return 0;
+  if (lse && n_splits != 1) return PMM_ERR_BAD_ARGUMENT;
   if (!pmm_decode_attention_tma_supported(Hq, Hkv, Dh, page_size) || !q_src || (k_src == nullptr) != (v_src == nullptr) ||
       !pool || !block_table || !positions || !out || !status || pool_pages <= 0 || !(scale > 0.f) || n_splits < 1 ||
       n_splits > 64 || Hkv > 65535 || reinterpret_cast<uintptr_t>(pool) % 16 || reinterpret_cast<uintptr_t>(out) % 8)
@@ -690,6 +695,7 @@ PMM_EXPORT int pmm_decode_attention_tma(const void* q_src, long long ldq, const 
   a.split_counter = split_counter;
   a.status = status;
   a.sink = sink;
+  a.lse = lse;
   return Dh == 64 ? pmm::launch_decode_attention<64>(map, a, n_seq, stream)
                   : pmm::launch_decode_attention<128>(map, a, n_seq, stream);
 }

@@ -9,6 +9,6 @@ extern "C" int pmm_flash_paged_attention(const void* q, const void* pool, const 
                                          float* part_o, float* part_ml, float scale, int window,
                                          int split_len, int n_splits, int page_size, int n_seq, int n_tiles,
                                          int tile_rows, int Hq, int Hkv, int Dh, int* split_counter,
-                                         const float* sink, cudaStream_t stream);
+                                         const float* sink, float* lse, cudaStream_t stream);
 extern "C" int pmm_flash_combine(const float* part_o, const float* part_ml, void* out, int n_rows,
                                  int n_splits, int Dh, int dtype, cudaStream_t stream);

@@ -48,6 +48,8 @@ struct FlashDecodeInputs {
   bf16* pool_w;           // the cache, writable
   int one_token;          // tile index == sequence index == token index
   const float* sink;      // [Hq] or nullptr: exp(sink[h]) joins every row's softmax denominator once
+  float* lse;             // [tokens, Hq, 2] or nullptr: with one key split, every row's (maximum in natural-log
+                          // units, sum of exponentials) beside its normalised result, for a later merge
 };
 
 // MT = row tiles of 16 per warp: 1 (64 rows a block) or 2 (128 rows a block, every K/V fragment
@@ -505,6 +507,8 @@ __global__ void __launch_bounds__(128)
         const int t = tok0 + r / G, hq = hk * G + r % G;
         if (n_splits == 1) {
           const float inv = l > 0.f ? 1.f / l : 0.f;
+          if (dec.lse != nullptr && (lane & 3) == 0)
+            *reinterpret_cast<float2*>(dec.lse + (static_cast<size_t>(t) * Hq + hq) * 2) = make_float2(m * kLn2, l);
           bf16* dst = out + (static_cast<size_t>(t) * Hq + hq) * DH;
 #pragma unroll
           for (int nt = 0; nt < NT_O; ++nt) {
@@ -571,6 +575,8 @@ __global__ void __launch_bounds__(128)
       if (n_splits == 1) {
         const float l = s_L[r];
         out[(static_cast<size_t>(t) * Hq + hq) * DH + d] = __float2bfloat16_rn(l > 0.f ? sum / l : 0.f);
+        if (dec.lse != nullptr && d == 0)
+          *reinterpret_cast<float2*>(dec.lse + (static_cast<size_t>(t) * Hq + hq) * 2) = make_float2(s_M[r] * kLn2, l);
       } else {
         const size_t pi = (static_cast<size_t>(t) * Hq + hq) * n_splits + z;
         part_o[pi * DH + d] = sum;
@@ -771,9 +777,11 @@ PMM_EXPORT int pmm_flash_paged_attention(const void* q, const void* pool, const 
                                          void* out, float* part_o, float* part_ml, float scale,
                                          int window, int split_len, int n_splits, int page_size,
                                          int n_seq, int n_tiles, int tile_rows, int Hq, int Hkv, int Dh,
-                                         int* split_counter, const float* sink, cudaStream_t stream) {
+                                         int* split_counter, const float* sink, float* lse, cudaStream_t stream) {
+  if (lse && n_splits != 1) return PMM_ERR_BAD_ARGUMENT;
   pmm::FlashDecodeInputs dec{};
   dec.sink = sink;
+  dec.lse = lse;
   return pmm::flash_dispatch(q, pool, block_table, max_blocks, positions, cu, out, part_o, part_ml, scale,
                              window, split_len, n_splits, page_size, n_seq, n_tiles, tile_rows, Hq, Hkv, Dh,
                              split_counter, dec, stream);
@@ -791,8 +799,9 @@ PMM_EXPORT int pmm_flash_decode_attention(const void* q_src, long long ldq, cons
                                           const int* block_table, int max_blocks, const int* positions,
                                           void* out, float* part_o, float* part_ml, float scale, int window,
                                           int split_len, int n_splits, int page_size, int n_seq, int Hq,
-                                          int Hkv, int Dh, int* split_counter, const float* sink,
+                                          int Hkv, int Dh, int* split_counter, const float* sink, float* lse,
                                           cudaStream_t stream) {
+  if (lse && n_splits != 1) return PMM_ERR_BAD_ARGUMENT;
   if (!q_src || (k_src == nullptr) != (v_src == nullptr) || Hkv <= 0 || Hq % Hkv || Hq / Hkv > 16)
     return PMM_ERR_BAD_ARGUMENT;
   if (n_splits > 1 && !split_counter) return PMM_ERR_BAD_ARGUMENT;  // the separate merge is not wired here
@@ -810,6 +819,7 @@ PMM_EXPORT int pmm_flash_decode_attention(const void* q_src, long long ldq, cons
   dec.pool_w = static_cast<pmm::bf16*>(pool);
   dec.one_token = 1;
   dec.sink = sink;
+  dec.lse = lse;
   return pmm::flash_dispatch(nullptr, pool, block_table, max_blocks, positions, nullptr, out, part_o, part_ml,
                              scale, window, split_len, n_splits, page_size, n_seq, n_seq, 16, Hq, Hkv, Dh,
                              split_counter, dec, stream);

@@ -74,7 +74,7 @@ PMM_EXPORT int pmm_attention_noalloc(const void* q, const void* pool, const int*
   if (n_splits == 1) {  // no partial results, so no scratch: the regular path allocates nothing either
     int rc1 = pmm_flash_paged_attention(q, pool, block_table, max_blocks, positions, cu, out, nullptr, nullptr, scale,
                                         window, split_len, 1, page_size, n_seq, n_tiles, tile_rows, Hq, Hkv, Dh,
-                                        nullptr, nullptr, stream);
+                                        nullptr, nullptr, nullptr, stream);
     return rc1 == 0 ? 0 : fail(rc1, "attention launch failed (code %lld)", rc1);
   }
   const long long rows = static_cast<long long>(n_tokens) * Hq;
@@ -90,7 +90,7 @@ PMM_EXPORT int pmm_attention_noalloc(const void* q, const void* pool, const int*
   float* part_ml = scratch + rows * n_splits * Dh;
   int rc = pmm_flash_paged_attention(q, pool, block_table, max_blocks, positions, cu, out, part_o, part_ml, scale,
                                      window, split_len, n_splits, page_size, n_seq, n_tiles, tile_rows, Hq, Hkv, Dh,
-                                     nullptr, nullptr, stream);
+                                     nullptr, nullptr, nullptr, stream);
   if (rc != 0) return fail(rc, "attention launch failed (code %lld)", rc);
   rc = pmm_flash_combine(part_o, part_ml, out, static_cast<int>(rows), n_splits, Dh, PMM_DTYPE_BF16, stream);
   if (rc != 0) return fail(rc, "merge launch failed (code %lld)", rc);

@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(kAtThreads, DH == 64 ? 2 : 1)
                         const int* __restrict__ cu, bf16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, float scale_log2, int window, int split_len, int n_splits,
                         int page_size, int n_seq, int Hq, int Hkv, int* __restrict__ split_counter,
-                        int* __restrict__ status, const float* __restrict__ sink) {
+                        int* __restrict__ status, const float* __restrict__ sink, float* __restrict__ lse) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int NSUB = DH / kAtDhBlock;            // sub-tiles of 64 head-size columns
@@ -395,6 +395,8 @@ __global__ void __launch_bounds__(kAtThreads, DH == 64 ? 2 : 1)
       }
       if (n_splits == 1) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        // (for a later merge with keys outside this launch's range: the row's maximum in natural-log units and sum)
+        if (lse != nullptr) *reinterpret_cast<float2*>(lse + (static_cast<size_t>(t) * Hq + hq) * 2) = make_float2(m_run * kLn2, l_run);
         bf16* dst = out + (static_cast<size_t>(t) * Hq + hq) * DH;
 #pragma unroll
         for (int c = 0; c < DH / 8; ++c) {
@@ -495,8 +497,9 @@ PMM_EXPORT int pmm_attention_tc(const void* q, const void* pool, long long pool_
                                 int max_blocks, const int* positions, const int* cu, void* out, float* part_o,
                                 float* part_ml, float scale, int window, int split_len, int n_splits, int page_size,
                                 int n_seq, int n_tiles, int Hq, int Hkv, int Dh, int* split_counter, int* status,
-                                const float* sink, cudaStream_t stream) {
+                                const float* sink, float* lse, cudaStream_t stream) {
   if (n_seq <= 0 || n_tiles <= 0) return 0;
+  if (lse && n_splits != 1) return PMM_ERR_BAD_ARGUMENT;
   if (!pmm_attention_tc_supported(Hq, Hkv, Dh, page_size) || !status || !(scale > 0.f) || n_splits < 1 ||
       n_splits > 64 || Hkv > 65535 || pool_pages <= 0 || reinterpret_cast<uintptr_t>(pool) % 16 ||
       reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(out) % 16)
@@ -526,6 +529,6 @@ PMM_EXPORT int pmm_attention_tc(const void* q, const void* pool, long long pool_
   pmm::launch_pdl(kern, grid, dim3(pmm::kAtThreads), smem, stream,
       static_cast<const pmm::bf16*>(q), map, block_table, max_blocks, positions, cu, static_cast<pmm::bf16*>(out), part_o,
       part_ml, scale * 1.4426950408889634f, window, split_len, n_splits, page_size, n_seq, Hq, Hkv, split_counter, status,
-      sink);
+      sink, lse);
   return pmm::launch_status();
 }

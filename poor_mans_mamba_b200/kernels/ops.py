@@ -63,6 +63,8 @@ _SIGNATURES = {
     "pmm_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "pmm_kept_first_merge": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int,
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_hc_mix_norm": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_normed_sum": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int,
@@ -83,22 +85,22 @@ _SIGNATURES = {
     "pmm_flash_supported": [c_int, c_int, c_int],
     "pmm_flash_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "pmm_l2_prefetch": [c_void_p, c_void_p, c_int, c_void_p],
     "pmm_attention_tc_supported": [c_int, c_int, c_int, c_int],
     "pmm_attention_tc": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                         c_void_p, c_void_p, c_void_p],
+                         c_void_p, c_void_p, c_void_p, c_void_p],
     "pmm_skinny_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "pmm_flash_decode_attention": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
                                    c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                   c_int, c_void_p, c_void_p, c_void_p],
+                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "pmm_decode_attention_tma_supported": [c_int, c_int, c_int, c_int],
     "pmm_decode_attention_tma": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_float,
                                  c_float, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                 c_void_p, c_void_p, c_void_p],
+                                 c_void_p, c_void_p, c_void_p, c_void_p],
     "pmm_flash_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_skinny_gemm": [c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int,
                         c_float, c_void_p, c_longlong, c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p,
@@ -917,9 +919,12 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
                     scratch: Optional[Tensor] = None, cu_seqlens: Optional[Tensor] = None,
                     new_lens: Optional[Sequence[int]] = None, use_tensor_cores: bool = True,
                     split_counter: Optional[Tensor] = None, tile_rows: Optional[int] = None,
-                    sink: Optional[Tensor] = None, keep_first: int = 0) -> None:
+                    sink: Optional[Tensor] = None, keep_first: int = 0, lse: Optional[Tensor] = None) -> None:
     """Causal attention of every token over keys lo..pos of its request in the paged cache.
     ``keep_first``: the request's first keep_first keys stay visible behind a window (at their true positions).
+    The float kernel walks both key ranges itself; the tensor-core kernel takes them with one key split and
+    ``lse`` (float32 [T, Hq, 2] scratch): it leaves every row's maximum and sum there and `kept_first_merge` adds
+    the kept keys.
     ``sink`` (one float per query head): the softmax's denominator also holds exp(sink[h]), a score
     without key or value.
     With ``cu_seqlens`` and ``new_lens`` (tokens per sequence, host values) a bfloat16 cache of a
@@ -955,7 +960,9 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
     if not (keep_first >= 0):
         raise KernelError("attention: keep_first must not be negative")
     flash = (use_tensor_cores and q.dtype == torch.bfloat16 and cu_seqlens is not None and new_lens is not None
-             and flash_supported(n_q_heads, n_kv_heads, head_dim) and (keep_first == 0 or window == 0))
+             and flash_supported(n_q_heads, n_kv_heads, head_dim)
+             and (keep_first == 0 or window == 0 or (lse is not None and n_splits == 1)))
+    keep = int(keep_first) if window > 0 else 0
     if flash:
         _i32(cu_seqlens, "attention: cu_seqlens")
         group = n_q_heads // n_kv_heads
@@ -974,17 +981,49 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
         _call("pmm_flash_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], positions.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), part_o,
               part_ml, float(softmax_scale), int(window), int(split_len), int(n_splits), pool.shape[2],
-              len(new_lens), n_tiles, int(tile_rows), n_q_heads, n_kv_heads, head_dim, counter, _ptr(sink), _stream())
+              len(new_lens), n_tiles, int(tile_rows), n_q_heads, n_kv_heads, head_dim, counter, _ptr(sink),
+              _lse_ptr(lse, T, n_q_heads) if keep > 0 else None, _stream())
+        if keep > 0:
+            kept_first_merge(q, pool, block_table, positions, seq_of, out, lse, n_q_heads, n_kv_heads, head_dim,
+                             softmax_scale, window, keep)
         if counter is not None:
             return
     else:
         _call("pmm_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], positions.data_ptr(), seq_of.data_ptr(), out.data_ptr(), part_o, part_ml,
               float(softmax_scale), int(window), int(split_len), int(n_splits), pool.shape[2], T, n_q_heads,
-              n_kv_heads, head_dim, _dt(q), _ptr(sink), int(keep_first) if window > 0 else 0, _stream())
+              n_kv_heads, head_dim, _dt(q), _ptr(sink), keep, _stream())
     if n_splits > 1:
         _call("pmm_flash_combine", part_o, part_ml, out.data_ptr(), T * n_q_heads, int(n_splits), head_dim,
               _dt(out), _stream())
+
+
+def _lse_ptr(lse: Optional[Tensor], T: int, n_q_heads: int) -> int:
+    if not (lse is not None and lse.is_cuda and lse.dtype == torch.float32 and lse.is_contiguous()
+            and lse.numel() >= 2 * T * n_q_heads):
+        raise KernelError("attention: kept first keys need float32 scratch [T, Hq, 2] for the rows' maxima and sums")
+    return lse.data_ptr()
+
+
+def kept_first_merge(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor, seq_of: Tensor, out: Tensor,
+                     lse: Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, softmax_scale: float, window: int,
+                     keep_first: int) -> None:
+    """``out`` [T, Hq*Dh] holds every row's attention over its window (and sink), ``lse`` [T, Hq, 2] that result's
+    maximum score and sum of exponentials: the request's first ``keep_first`` keys that a row's window has left
+    behind are added, and the row becomes the softmax over both sets of keys."""
+    _cuda(q, pool, block_table, positions, seq_of, out, lse)
+    T = q.shape[0]
+    if not (q.is_contiguous() and out.is_contiguous() and q.shape == (T, n_q_heads * head_dim) and out.shape == q.shape
+            and q.dtype == out.dtype == pool.dtype):
+        raise KernelError("kept_first_merge: q and out must be contiguous [T, Hq*Dh] of the pool's type")
+    if not (pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == n_kv_heads * head_dim and pool.is_contiguous()):
+        raise KernelError("kept_first_merge: pool must be contiguous [pages, 2, page_size, Hkv*Dh]")
+    _i32(block_table, "kept_first_merge: block_table")
+    _i32(positions, "kept_first_merge: positions")
+    _i32(seq_of, "kept_first_merge: seq_of")
+    _call("pmm_kept_first_merge", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+          positions.data_ptr(), seq_of.data_ptr(), out.data_ptr(), _lse_ptr(lse, T, n_q_heads), float(softmax_scale),
+          int(window), int(keep_first), pool.shape[2], T, n_q_heads, n_kv_heads, head_dim, _dt(q), _stream())
 
 
 # Decode attention with TMA tile loads where the sizes allow (PMM_TMA_DECODE=0: cp.async gathers throughout).
@@ -1001,12 +1040,21 @@ def flash_decode_attention(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], 
                            positions: Tensor, out: Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
                            softmax_scale: float, window: int = 0, n_splits: int = 1, split_len: int = 0,
                            scratch: Optional[Tensor] = None, split_counter: Optional[Tensor] = None,
-                           sink: Optional[Tensor] = None) -> None:
+                           sink: Optional[Tensor] = None, keep_first: int = 0, lse: Optional[Tensor] = None,
+                           seq_of: Optional[Tensor] = None) -> None:
     """A decode step's attention straight from the projections (token t is sequence t's one new
     token): scales and rotates queries and new keys, writes the new keys and values into their
     cache pages and attends over the cache, in one launch.  ``k``/``v`` None: the cache has them.
-    ``sink``: see paged_attention."""
+    ``sink``: see paged_attention.  ``keep_first`` > 0 behind a window: one key split, ``lse`` scratch and
+    ``seq_of`` (token -> sequence, here 0, 1, 2, ...), and queries that are rotated already (k and v None)."""
     _cuda(q, k, v, inv_freq, pool, block_table, positions, out, scratch, split_counter, sink)
+    keep = int(keep_first) if window > 0 else 0
+    lse_ptr = None
+    if keep > 0:
+        if not (n_splits == 1 and k is None and v is None and inv_freq is None and seq_of is not None
+                and q_scale == 1.0 and q.is_contiguous()):
+            raise KernelError("decode attention: kept first keys take one key split and prepared queries")
+        lse_ptr = _lse_ptr(lse, q.shape[0], n_q_heads)
     _f32vec(sink, n_q_heads, "decode attention: sink")
     n_seq = q.shape[0]
     kv_dim = n_kv_heads * head_dim
@@ -1050,12 +1098,18 @@ def flash_decode_attention(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], 
               float(v_scale), _ptr(inv_freq), pool.data_ptr(), pool.shape[0], block_table.data_ptr(),
               block_table.shape[1], positions.data_ptr(), out.data_ptr(), part_o, part_ml, float(softmax_scale),
               int(window), int(split_len), int(n_splits), pool.shape[2], n_seq, n_q_heads, n_kv_heads, head_dim, counter,
-              _tc_status(q.device).data_ptr(), _ptr(sink), _stream())
+              _tc_status(q.device).data_ptr(), _ptr(sink), lse_ptr, _stream())
+        if keep > 0:
+            kept_first_merge(q, pool, block_table, positions, seq_of, out, lse, n_q_heads, n_kv_heads, head_dim,
+                             softmax_scale, window, keep)
         return
     _call("pmm_flash_decode_attention", q.data_ptr(), ldq, _ptr(k), ldk, _ptr(v), ldv, float(q_scale), float(k_scale),
           float(v_scale), _ptr(inv_freq), pool.data_ptr(), block_table.data_ptr(), block_table.shape[1],
           positions.data_ptr(), out.data_ptr(), part_o, part_ml, float(softmax_scale), int(window), int(split_len),
-          int(n_splits), pool.shape[2], n_seq, n_q_heads, n_kv_heads, head_dim, counter, _ptr(sink), _stream())
+          int(n_splits), pool.shape[2], n_seq, n_q_heads, n_kv_heads, head_dim, counter, _ptr(sink), lse_ptr, _stream())
+    if keep > 0:
+        kept_first_merge(q, pool, block_table, positions, seq_of, out, lse, n_q_heads, n_kv_heads, head_dim,
+                         softmax_scale, window, keep)
 
 
 SKINNY_MAX_TOKENS = 64  # the weight-streaming products take up to 64 tokens (where their shared memory fits)
@@ -1425,13 +1479,18 @@ def attention_tc(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor
                  new_lens: Sequence[int], out: Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
                  softmax_scale: float, window: int = 0, n_splits: int = 1, split_len: int = 0,
                  scratch: Optional[Tensor] = None, split_counter: Optional[Tensor] = None,
-                 sink: Optional[Tensor] = None) -> None:
+                 sink: Optional[Tensor] = None, keep_first: int = 0, lse: Optional[Tensor] = None,
+                 seq_of: Optional[Tensor] = None) -> None:
     """Causal attention of prompt portions over the paged cache on the fifth-generation tensor cores
     (TMA tiles straight from the pages, scores and P V in tensor memory, one thread per query row
     for the softmax).  Same contract as paged_attention with rotated queries and a cache that holds
-    the step's keys already; 128 rows of (token, query head of a group) per block."""
+    the step's keys already; 128 rows of (token, query head of a group) per block.  ``keep_first`` > 0 behind a
+    window: one key split, ``lse`` scratch and ``seq_of``, as in paged_attention."""
     _cuda(q, pool, block_table, positions, cu_seqlens, out, scratch, split_counter)
     T = q.shape[0]
+    keep = int(keep_first) if window > 0 else 0
+    if keep > 0 and not (n_splits == 1 and seq_of is not None):
+        raise KernelError("attention_tc: kept first keys take one key split and seq_of")
     if not (q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
             and q.is_contiguous() and out.is_contiguous() and q.shape == (T, n_q_heads * head_dim) and out.shape == q.shape):
         raise KernelError("attention_tc: q and out must be contiguous bfloat16 [T, Hq*Dh]")
@@ -1462,7 +1521,10 @@ def attention_tc(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor
     _call("pmm_attention_tc", q.data_ptr(), pool.data_ptr(), pool.shape[0], block_table.data_ptr(), block_table.shape[1],
           positions.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), part_o, part_ml, float(softmax_scale), int(window),
           int(split_len), int(n_splits), pool.shape[2], len(new_lens), n_tiles, n_q_heads, n_kv_heads, head_dim, counter,
-          _tc_status(q.device).data_ptr(), _ptr(sink), _stream())
+          _tc_status(q.device).data_ptr(), _ptr(sink), _lse_ptr(lse, T, n_q_heads) if keep > 0 else None, _stream())
+    if keep > 0:
+        kept_first_merge(q, pool, block_table, positions, seq_of, out, lse, n_q_heads, n_kv_heads, head_dim, softmax_scale,
+                         window, keep)
 
 
 def silu_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:

@@ -54,36 +54,45 @@ class PagedSoftmaxAttention(_StackedInput):
         counter = self._split_counter
         # (the tensor-core kernels take the row maximum before the scale is applied: positive scales only)
         bf16 = q_rot.dtype == torch.bfloat16 and counter is not None and self.scale > 0.0
+        # Kept first keys behind a window: the tensor-core kernels attend over the window with one key split and
+        # leave every row's maximum and sum in `lse`; a small launch then adds the kept keys that the window has
+        # left (the float kernel walks both key ranges itself).
         keep = self.keep_first if self.window > 0 else 0
-        if keep > 0:
-            bf16 = False  # kept first keys behind a window: the float kernel walks the two key ranges
+        lse = ws.alloc((T, H, 2), torch.float32) if keep > 0 and bf16 else None
 
         def scratch_for(n_splits):
             return ws.alloc((K.attention_scratch_floats(T, H, Dp, n_splits),), torch.float32) if n_splits > 1 else None
 
         if bf16 and ctx.decode_only and K.flash_decode_supported(H, G, Dp):
             n_splits, split_len = plan_key_splits(H, G, Dp, self.window, ctx.new_lens, ctx.kv_len_bound, q_rot.dtype)
+            if keep > 0:
+                n_splits, split_len = 1, 0
             if n_splits <= 64 and counter.numel() >= T * G:
                 K.flash_decode_attention(q_rot, None, None, 1.0, 1.0, 1.0, None, kv.pool, kv.block_table, ctx.positions,
                                          attn, H, G, Dp, self.scale, window=self.window, n_splits=n_splits,
                                          split_len=split_len, scratch=scratch_for(n_splits), split_counter=counter,
-                                         sink=self.sink)
+                                         sink=self.sink, keep_first=keep, lse=lse, seq_of=ctx.seq_of)
                 return
         if (bf16 and not ctx.decode_only and sum(ctx.new_lens) >= _TC_FROM_TOKENS
                 and K.attention_tc_supported(H, G, Dp, kv.pool.shape[2])):
             n_splits, split_len = plan_key_splits_tc(H, G, self.window, ctx.new_lens, ctx.kv_len_bound)
+            if keep > 0:
+                n_splits, split_len = 1, 0
             per_tile = 128 // (H // G)
             tiles = sum((n + per_tile - 1) // per_tile for n in ctx.new_lens)
             if n_splits <= 64 and counter.numel() >= tiles * G:
                 K.attention_tc(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.cu_seqlens, ctx.new_lens, attn, H, G, Dp,
                                self.scale, window=self.window, n_splits=n_splits, split_len=split_len,
-                               scratch=scratch_for(n_splits), split_counter=counter, sink=self.sink)
+                               scratch=scratch_for(n_splits), split_counter=counter, sink=self.sink, keep_first=keep,
+                               lse=lse, seq_of=ctx.seq_of)
                 return
         n_splits, split_len = plan_key_splits(H, G, Dp, self.window, ctx.new_lens, ctx.kv_len_bound, q_rot.dtype)
+        if lse is not None and K.flash_supported(H, G, Dp):
+            n_splits, split_len = 1, 0
         K.paged_attention(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.seq_of, attn, H, G, Dp, self.scale,
                           window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch_for(n_splits),
                           cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens, split_counter=counter, sink=self.sink,
-                          keep_first=keep)
+                          keep_first=keep, lse=lse)
 
 
 class WindowSinkAttention(PagedSoftmaxAttention):

@@ -249,3 +249,70 @@ def test_window_with_kept_first_tokens_and_one_more_in_the_denominator(dtype, wi
         K.paged_attention(q[t].reshape(1, -1).to(DEV, dtype), pool, row.view(1, -1).to(DEV), i32([p]), i32([0]), out, H, G, d,
                           scale, window=window, sink=sink, keep_first=keep)
         close(out.view(H, d), want, dtype, f"query at {p}", f32=3e-5)
+
+
+@pytest.mark.parametrize("d,window,keep", [(64, 96, 4), (128, 200, 70), (64, 64, 1), (32, 40, 5)])
+def test_kept_first_tokens_on_the_tensor_core_kernels(d, window, keep):
+    """bfloat16, pages of 64: a portion of 300 tokens at positions 400..699 through the tcgen05 kernel (head sizes
+    64 and 128) and the mma.sync kernel, and the last token alone through the decode kernels; the window is attended
+    by the tensor-core kernel, the kept first keys that it has left are added by the merge launch.  Key 0 and
+    the keys at both edges of the first row's window are loud."""
+    H, G, n, page, scale, dtype = 4, 2, 700, 64, 0.25, torch.bfloat16
+    keys, vals = rnd(n, G, d, seed=1), rnd(n, G, d, seed=2)
+    t0 = 400
+    T = n - t0
+    q = rnd(T, H, d, seed=3)
+    keys[[0, keep - 1, keep, t0 - window, t0 - window + 1], :, 3] = 4.0
+    q[:, :, 3] = 2.0
+    n_blocks = (n + page - 1) // page
+    table = torch.randperm(n_blocks, generator=torch.Generator().manual_seed(5)).to(torch.int32)
+    pool = torch.full((n_blocks + 1, 2, page, G * d), 9.0, dtype=dtype, device=DEV)
+    for j in range(n):
+        pool[int(table[j // page]), 0, j % page] = keys[j].reshape(-1).to(dtype)
+        pool[int(table[j // page]), 1, j % page] = vals[j].reshape(-1).to(dtype)
+    sink = torch.zeros(H, dtype=torch.float32, device=DEV)
+    mask = P.window_mask(n, window, keep)
+    k_h, v_h = keys.double().repeat_interleave(H // G, dim=1), vals.double().repeat_interleave(H // G, dim=1)
+    want = torch.zeros(T, H, d, dtype=torch.float64)
+    for t in range(T):
+        p = t0 + t
+        sc = torch.einsum("hd,jhd->hj", q[t].double(), k_h[:p + 1]) * scale
+        sc = sc.masked_fill(~mask[p, :p + 1][None, :], -math.inf)
+        mx = sc.max(dim=1, keepdim=True).values.clamp(min=0.0)
+        e = torch.exp(sc - mx)
+        want[t] = torch.einsum("hj,jhd->hd", e / (torch.exp(-mx) + e.sum(dim=1, keepdim=True)), v_h[:p + 1])
+    kept_blocks = (keep + page - 1) // page
+
+    def row_for(first_pos):     # pages between the kept ones and the window of the step's first token are gone
+        row = table.clone()
+        row[kept_blocks:max(kept_blocks, max(0, first_pos - window + 1) // page)] = n_blocks
+        return row.view(1, -1).to(DEV)
+
+    qd = q.reshape(T, H * d).to(DEV, dtype)
+    positions, seq_of, cu = i32(list(range(t0, n))), i32([0] * T), i32([0, T])
+    counter = torch.zeros(64, dtype=torch.int32, device=DEV)
+    ran = 0
+    if K.attention_tc_supported(H, G, d, page):
+        out, lse = torch.empty(T, H * d, dtype=dtype, device=DEV), torch.empty(T, H, 2, dtype=torch.float32, device=DEV)
+        K.attention_tc(qd, pool, row_for(t0), positions, cu, [T], out, H, G, d, scale, window=window, sink=sink,
+                       keep_first=keep, lse=lse, seq_of=seq_of, split_counter=counter)
+        close(out.view(T, H, d), want, dtype, "tcgen05 prompt kernel")
+        ran += 1
+    if K.flash_supported(H, G, d):
+        out, lse = torch.empty(T, H * d, dtype=dtype, device=DEV), torch.empty(T, H, 2, dtype=torch.float32, device=DEV)
+        K.paged_attention(qd, pool, row_for(t0), positions, seq_of, out, H, G, d, scale, window=window, cu_seqlens=cu,
+                          new_lens=[T], sink=sink, keep_first=keep, lse=lse, split_counter=counter)
+        close(out.view(T, H, d), want, dtype, "mma.sync prompt kernel")
+        ran += 1
+    if K.flash_decode_supported(H, G, d):
+        out, lse = torch.empty(1, H * d, dtype=dtype, device=DEV), torch.empty(1, H, 2, dtype=torch.float32, device=DEV)
+        K.flash_decode_attention(qd[T - 1:], None, None, 1.0, 1.0, 1.0, None, pool, row_for(n - 1), positions[T - 1:], out, H, G,
+                                 d, scale, window=window, sink=sink, keep_first=keep, lse=lse, seq_of=i32([0]),
+                                 split_counter=counter)
+        close(out.view(1, H, d), want[T - 1:], dtype, "decode kernel")
+        ran += 1
+    assert ran >= 2
+    # the same without the scratch: the float kernel walks both key ranges itself
+    out = torch.empty(T, H * d, dtype=dtype, device=DEV)
+    K.paged_attention(qd, pool, row_for(t0), positions, seq_of, out, H, G, d, scale, window=window, sink=sink, keep_first=keep)
+    close(out.view(T, H, d), want, dtype, "float kernel")
