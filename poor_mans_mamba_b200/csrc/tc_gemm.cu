@@ -43,7 +43,13 @@ constexpr size_t kTcSmem = static_cast<size_t>(kTcStages) * (kTcABytes + kTcBByt
 // kTcClampedGlu: the gate and up layout of kTcSwiglu with the activation
 //   g = min(gate, limit); u = clamp(up, -limit, limit); act = g * sigmoid(alpha * g) * (u + shift)
 // (limit rides in gate_mult's place).
-enum { kTcPlain = 0, kTcSwiglu = 1, kTcClampedGlu = 2 };
+// kTcGeluGlu: the same layout with act = gelu_tanh(gate * gate_mult) * up, the tanh form of GELU,
+//   gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) = z / (1 + exp(-2 sqrt(2/pi) (z + 0.044715 z^3))).
+enum { kTcPlain = 0, kTcSwiglu = 1, kTcClampedGlu = 2, kTcGeluGlu = 3 };
+
+__device__ __forceinline__ float gelu_tanh_fast(float z) {
+  return __fdividef(z, 1.f + __expf(-1.5957691216057308f * (z + 0.044715f * z * z * z)));
+}
 
 // kind::f16 instruction descriptor: float accumulate, bfloat16 A and B, both K-major, N, M.
 constexpr unsigned kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kTcN >> 3) << 17) | ((kTcMH >> 4) << 24);
@@ -183,6 +189,10 @@ __global__ void __launch_bounds__(kTcThreads)
                   const float u1 = fminf(fmaxf(__uint_as_float(u[j + 2 * e + 1]), -gate_mult), gate_mult);
                   p2[e] = __floats2bfloat162_rn(__fdividef(g0, 1.f + __expf(-act_alpha * g0)) * (u0 + act_shift),
                                                 __fdividef(g1, 1.f + __expf(-act_alpha * g1)) * (u1 + act_shift));
+                } else if (MODE == kTcGeluGlu) {
+                  const float g0 = __uint_as_float(g[j + 2 * e]) * gate_mult, g1 = __uint_as_float(g[j + 2 * e + 1]) * gate_mult;
+                  p2[e] = __floats2bfloat162_rn(gelu_tanh_fast(g0) * __uint_as_float(u[j + 2 * e]),
+                                                gelu_tanh_fast(g1) * __uint_as_float(u[j + 2 * e + 1]));
                 } else {
                   const float g0 = __uint_as_float(g[j + 2 * e]) * gate_mult, g1 = __uint_as_float(g[j + 2 * e + 1]) * gate_mult;
                   p2[e] = __floats2bfloat162_rn(silu_fast(g0) * __uint_as_float(u[j + 2 * e]),
@@ -248,6 +258,7 @@ PMM_EXPORT int pmm_tc_gemm_supported(int mode, int K, int n_out, long long ldx, 
 
 // mode 1: out[T, F] = silu((x Wg^T) * gate_mult) * (x Wu^T) with w = [Wg; Wu] ([2F, K]).
 // mode 2: the same layout with the clamped gated activation (limit = gate_mult, act_alpha, act_shift).
+// mode 3: the same layout with gelu_tanh on the gate (gate_mult as in mode 1).
 // mode 0: out[T, N] = x w^T with w [N, K].  status: one int, stays 0 unless a bounded wait gave up.
 namespace pmm {
 template <int MODE>
@@ -266,7 +277,7 @@ PMM_EXPORT int pmm_tc_gemm_act(int mode, const void* x, long long ldx, const voi
                                int K, int n_out, float gate_mult, float act_alpha, float act_shift, int* status,
                                cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (mode < 0 || mode > 2 || !pmm_tc_gemm_supported(mode, K, n_out, ldx, ld_out) || !status) return PMM_ERR_BAD_ARGUMENT;
+  if (mode < 0 || mode > 3 || !pmm_tc_gemm_supported(mode, K, n_out, ldx, ld_out) || !status) return PMM_ERR_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(w) % 16 || reinterpret_cast<uintptr_t>(out) % 16)
     return PMM_ERR_BAD_ARGUMENT;
   CUtensorMap map_x, map_w;
@@ -278,6 +289,9 @@ PMM_EXPORT int pmm_tc_gemm_act(int mode, const void* x, long long ldx, const voi
   if (mode == pmm::kTcSwiglu)
     return pmm::launch_tc_gemm<pmm::kTcSwiglu>(map_x, map_w, grid, out, ld_out, T, K, n_out, gate_mult, act_alpha, act_shift,
                                                status, stream);
+  if (mode == pmm::kTcGeluGlu)
+    return pmm::launch_tc_gemm<pmm::kTcGeluGlu>(map_x, map_w, grid, out, ld_out, T, K, n_out, gate_mult, act_alpha, act_shift,
+                                                status, stream);
   if (mode == pmm::kTcClampedGlu)
     return pmm::launch_tc_gemm<pmm::kTcClampedGlu>(map_x, map_w, grid, out, ld_out, T, K, n_out, gate_mult, act_alpha,
                                                    act_shift, status, stream);

@@ -1442,6 +1442,19 @@ def tc_gemm_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) ->
           float(gate_mult), _tc_status(x.device).data_ptr(), _stream())
 
 
+def tc_gemm_gelu_glu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) -> None:
+    """out[T, F] = gelu_tanh((x Wg^T) * gate_mult) * (x Wu^T), gate_up = [Wg; Wu]: the tcgen05 launch of
+    `tc_gemm_swiglu` with the tanh form of GELU in its epilogue."""
+    _cuda(x, gate_up, out)
+    T, K = x.shape
+    F = gate_up.shape[0] // 2
+    if not (gate_up.shape == (2 * F, K) and out.shape == (T, F) and out.is_contiguous() and out.dtype == torch.bfloat16
+            and tc_gemm_supported(x, gate_up, F, True)):
+        raise KernelError("tc_gemm_gelu_glu: sizes or alignment outside what the kernel takes")
+    _call("pmm_tc_gemm_act", 3, x.data_ptr(), x.stride(0), gate_up.data_ptr(), out.data_ptr(), out.stride(0), T, K, F,
+          float(gate_mult), 0.0, 0.0, _tc_status(x.device).data_ptr(), _stream())
+
+
 def tc_gemm_clamped_glu(x: Tensor, gate_up: Tensor, limit: float, alpha: float, shift: float, out: Tensor) -> None:
     """out[T, F] = g * sigmoid(alpha g) * (u + shift), g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit), with
     gate_up = [Wg; Wu] ([2F, K]): one tcgen05 launch, the activation in its epilogue."""

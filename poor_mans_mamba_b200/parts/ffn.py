@@ -61,9 +61,13 @@ class SwiGLU(FeedForward):
         act = ctx.workspace.alloc((T, f), x.dtype)
         tiles = ((T + 255) // 256) * (f // 128)
         if self.gelu:
-            gu = ctx.workspace.alloc((T, 2 * f), x.dtype)
-            streaming.linear(x, self.gate_up, gu, ctx)
-            K.gelu_tanh_mul(gu, self.gate_multiplier, act)
+            if (_TC_ENABLED and tiles >= _TC_FROM_TILES and x.dtype == torch.bfloat16
+                    and K.tc_gemm_supported(x, self.gate_up, f, True)):
+                K.tc_gemm_gelu_glu(x, self.gate_up, self.gate_multiplier, act)  # the activation in the product's epilogue
+            else:
+                gu = ctx.workspace.alloc((T, 2 * f), x.dtype)
+                streaming.linear(x, self.gate_up, gu, ctx)
+                K.gelu_tanh_mul(gu, self.gate_multiplier, act)
             streaming.linear(act, self.down, out, ctx)
             return
         if streaming.swiglu(x, self.gate_up, self.gate_multiplier, act, ctx):

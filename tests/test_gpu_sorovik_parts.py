@@ -96,6 +96,21 @@ def test_gate_with_the_tanh_form_of_gelu(dtype, F):
     assert torch.allclose(P.gelu_tanh(z), torch.tensor(by_hand, dtype=torch.float64))
 
 
+def test_gelu_gate_in_the_epilogue_of_the_tensor_core_product():
+    """The dense feed-forward's [gate | up] product of a prompt step with the activation in its epilogue, against
+    the product followed by the activation launch and against the plain functions."""
+    T, D, F = 600, 320, 384
+    x, w = rnd(T, D, seed=1).to(DEV, torch.bfloat16), rnd(2 * F, D, seed=2, scale=D ** -0.5 * 2).to(DEV, torch.bfloat16)
+    if not K.tc_gemm_supported(x, w, F, True):
+        pytest.skip("sizes the tcgen05 product does not take")
+    out = torch.empty(T, F, dtype=torch.bfloat16, device=DEV)
+    K.tc_gemm_gelu_glu(x, w, 1.0, out)
+    torch.cuda.synchronize()
+    assert K.tc_gemm_status(x.device) == 0
+    gu = x.double().cpu() @ w.double().cpu().t()
+    close(out, P.gelu_tanh(gu[:, :F]) * gu[:, F:], torch.bfloat16, "gelu gate in the epilogue")
+
+
 @pytest.mark.parametrize("E,top,groups,keep", [(8, 3, 2, 1), (6, 2, 3, 2), (12, 5, 6, 3), (9, 3, 9, 4), (4, 4, 1, 1),
                                                (16, 1, 4, 1), (5, 2, 1, 1), (64, 6, 8, 3)])
 @pytest.mark.parametrize("T", [7, 700])
