@@ -552,8 +552,9 @@ def gikovik_config(falcon, mixer_sizes, ff_sizes, layers):
 # width, layers, vocabulary, experts, experts a token and expert widths).  Of every four layers the first and the
 # third are latent layers with rows of their own (96 latent entries beside 32 rotated ones: a cache row of 128), the
 # second is an attention layer with Falcon-H1's head counts and head size, and the fourth reads the third's rows.
-# Windows of 1,024 tokens; the attention layers keep the first four.
-def sorovik_config(falcon, mixer_sizes, ff_sizes, layers):
+# Windows of 1,024 tokens; the attention layers keep the first four.  The first layer's feed-forward is dense
+# (`dense_ff` wide, gated by the tanh form of GELU), the others are routed.
+def sorovik_config(falcon, mixer_sizes, ff_sizes, layers, dense_ff):
     experts, top, expert_ff, _ = ff_sizes
     heads, dim, vdim, _ = mixer_sizes
     hd = falcon["head_dim"]
@@ -565,12 +566,13 @@ def sorovik_config(falcon, mixer_sizes, ff_sizes, layers):
            "expert": {"ff": expert_ff}}
     out = []
     for i in range(layers):
+        ffn = {"kind": "dense", "ff": dense_ff} if i == 0 else mlp
         if i % 4 == 1:
-            out.append({"type": "attention", "mixer": att, "mlp": mlp})
+            out.append({"type": "attention", "mixer": att, "mlp": ffn})
         elif i % 4 == 3:
-            out.append({"type": "latent_attention", "mixer": dict(lat, kv_from=i - 1), "mlp": mlp})
+            out.append({"type": "latent_attention", "mixer": dict(lat, kv_from=i - 1), "mlp": ffn})
         else:
-            out.append({"type": "latent_attention", "mixer": lat, "mlp": mlp})
+            out.append({"type": "latent_attention", "mixer": lat, "mlp": ffn})
     return {"architecture": "Sorovik", "vocab": falcon["vocab_size"], "width": falcon["hidden_size"], "norm": {"eps": 1e-6},
             "layers": out}
 
@@ -590,7 +592,7 @@ def compare_workload(args, peaks) -> int:
     falcon["num_hidden_layers"] = layers
     vocab = falcon["vocab_size"]
     if args.design == "sorovik":
-        configs = {"sorovik": sorovik_config(falcon, GIKOVIK_MIXER[args.sizes], TAFESUN_FF[args.sizes], layers),
+        configs = {"sorovik": sorovik_config(falcon, GIKOVIK_MIXER[args.sizes], TAFESUN_FF[args.sizes], layers, ff),
                    "tafesun": tafesun_config(falcon, TAFESUN_FF[args.sizes], layers),
                    "gikovik": gikovik_config(falcon, GIKOVIK_MIXER[args.sizes], TAFESUN_FF[args.sizes], layers)}
         design_sizes = {"routed_ff": dict(zip(("experts", "top", "expert_ff", "shared_ff"), TAFESUN_FF[args.sizes])),

@@ -167,6 +167,71 @@ __global__ void add_postnorm_rmsnorm_kernel(float* __restrict__ h, const S* __re
   for (int i = threadIdx.x; i < D; i += blockDim.x) stf(o + i, buf[i] * inv * w[i]);
 }
 
+// The same for widths that are a multiple of 4: four elements per thread and access.
+template <typename S>
+__global__ void add_postnorm_rmsnorm_vec_kernel(float* __restrict__ h, const S* __restrict__ a, float sa,
+                                                const S* __restrict__ b, float sb, const float* __restrict__ post_w,
+                                                float post_eps, const float* __restrict__ w, float eps,
+                                                S* __restrict__ out, const int* __restrict__ rows, int D) {
+  extern __shared__ float buf[];
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const size_t src = static_cast<size_t>(rows ? rows[r] : r) * D;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) {
+    float4 s = ld4(a + src + i);
+    s.x *= sa; s.y *= sa; s.z *= sa; s.w *= sa;
+    if (b) {
+      const float4 x = ld4(b + src + i);
+      s.x += sb * x.x; s.y += sb * x.y; s.z += sb * x.z; s.w += sb * x.w;
+    }
+    *reinterpret_cast<float4*>(buf + i) = s;
+    ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  }
+  // (the stream's row is asked for before the reduction, so that its latency hides behind it: the first four
+  // pieces of a thread, which is all of them up to a width of 16 pieces a thread)
+  float4 hv[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int i = (threadIdx.x + c * blockDim.x) * 4;
+    hv[c] = (h && i < D) ? ld4(h + src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const float inv_p = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(D) + post_eps);
+  float sv = 0.f;
+  auto join = [&](int i, float4 x) {
+    const float4 s = *reinterpret_cast<const float4*>(buf + i);
+    const float4 g = ld4(post_w + i);
+    float4 v = make_float4(s.x * inv_p * g.x, s.y * inv_p * g.y, s.z * inv_p * g.z, s.w * inv_p * g.w);
+    if (h) {
+      v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+      if (!rows) st4(h + src + i, v);
+    }
+    *reinterpret_cast<float4*>(buf + i) = v;
+    sv += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  };
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int i = (threadIdx.x + c * blockDim.x) * 4;
+    if (i < D) join(i, hv[c]);
+  }
+  for (int i = (threadIdx.x + 4 * blockDim.x) * 4; i < D; i += blockDim.x * 4)
+    join(i, h ? ld4(h + src + i) : make_float4(0.f, 0.f, 0.f, 0.f));
+  if (!out) return;
+  S* o = out + static_cast<size_t>(r) * D;
+  if (!w) {
+    for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) st4(o + i, *reinterpret_cast<const float4*>(buf + i));
+    return;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sv, red) / static_cast<float>(D) + eps);
+  for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(buf + i);
+    const float4 g = ld4(w + i);
+    st4(o + i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+  }
+}
+
 __global__ void scale_f32_kernel(float* __restrict__ x, float s, size_t n) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) x[i] *= s;
@@ -223,8 +288,10 @@ PMM_EXPORT int pmm_add_postnorm_rmsnorm(void* h, const void* a, float sa, const 
   const size_t smem = static_cast<size_t>(D) * sizeof(float);
   if (smem > 200 * 1024) return PMM_ERR_BAD_ARGUMENT;
   const int threads = D >= 1024 ? 256 : 128;
+  auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec = D % 4 == 0 && aligned(h) && aligned(a) && aligned(b) && aligned(out) && aligned(w) && aligned(post_w);
   PMM_DISPATCH_DTYPE(dtype, S, {
-    auto kern = pmm::add_postnorm_rmsnorm_kernel<S>;
+    auto kern = vec ? pmm::add_postnorm_rmsnorm_vec_kernel<S> : pmm::add_postnorm_rmsnorm_kernel<S>;
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
       if (e != cudaSuccess) return static_cast<int>(e);
