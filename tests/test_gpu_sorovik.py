@@ -273,6 +273,26 @@ def test_options_that_one_model_leaves_equal(tmp_path):
                 check_rows(out[i], ref, dtype, f"options {dtype} seq {i}")
 
 
+def test_sizes_that_are_multiples_of_nothing(tmp_path):
+    """A width that is no multiple of 4, head sizes that are no multiples of 8, a latent of 6 entries beside 2
+    rotated ones, a convolution of 6 taps, 7 experts in one group, an odd vocabulary: the scalar forms of the
+    kernels and the float products."""
+    cfg = {"architecture": "Sorovik", "vocab": 77, "width": 50, "norm": {"eps": 1e-5}, "layers": [
+        C.layer(C.attention(3, 3, 10, 0.3, conv=6, rot=(6, 40.0), window=7, keep_first=2), C.moe(7, 3, 9)),
+        C.layer(C.latent(3, 5, 2, 7, 6, 0.4, 2, 30.0, window=11), C.dense(33)),
+        C.layer(C.latent(2, 9, 2, 3, 6, 0.3, 2, 30.0, window=19, kv_from=1), C.moe(6, 2, 10, groups=(3, 2))),
+    ]}
+    case = Case(cfg, tmp_path, lengths=(45, 3), seed=13)
+    seqs = case.seqs
+    for dtype in ("float32", "bfloat16"):
+        d, weights, refs = case.of(dtype)
+        for script in (H.script_whole(seqs), H.script_portions(seqs, seed=6), H.script_tail_one_by_one(seqs, tail=25)):
+            runner = H.make_runner(d, dtype, page_size=16, num_pages=8, num_slots=1)
+            out = H.run_script(runner, seqs, script)
+            for i, ref in enumerate(refs):
+                check_rows(out[i], ref, dtype, f"odd sizes {dtype} seq {i}")
+
+
 def test_greedy_generation_through_the_engine(case):
     """Engine.generate (scheduler, sampler, decode graphs) against greedy decoding with the plain
     implementation, float32; bfloat16 with graphs against bfloat16 step by step."""
