@@ -38,7 +38,7 @@ def i32(values):
 
 # ----------------------------------------------------------------------------- norms
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("D", [44, 72, 320, 1030])
+@pytest.mark.parametrize("D", [44, 72, 328, 1030])
 def test_embedding_with_its_norm(dtype, D):
     V, eps = 50, 1e-3
     table, w = rnd(V, D, seed=1, scale=3.0), rnd(D, seed=2) * 0.2 + 1.0
@@ -49,7 +49,7 @@ def test_embedding_with_its_norm(dtype, D):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("D,branches", [(44, 1), (72, 2), (320, 1), (1030, 2)])
+@pytest.mark.parametrize("D,branches", [(44, 1), (72, 2), (328, 1), (1030, 2)])
 def test_post_norm_of_a_sublayer_and_norm_of_the_stream_in_one_launch(dtype, D, branches):
     """x <- x + rms(sum of branches) * w_post, out = rms(x) * w: for all rows, for chosen rows (the stream is
     then left alone), without a following norm, and without a stream."""
@@ -99,7 +99,7 @@ def test_gate_with_the_tanh_form_of_gelu(dtype, F):
 def test_gelu_gate_in_the_epilogue_of_the_tensor_core_product():
     """The dense feed-forward's [gate | up] product of a prompt step with the activation in its epilogue, against
     the product followed by the activation launch and against the plain functions."""
-    T, D, F = 600, 320, 384
+    T, D, F = 600, 448, 512
     x, w = rnd(T, D, seed=1).to(DEV, torch.bfloat16), rnd(2 * F, D, seed=2, scale=D ** -0.5 * 2).to(DEV, torch.bfloat16)
     if not K.tc_gemm_supported(x, w, F, True):
         pytest.skip("sizes the tcgen05 product does not take")
