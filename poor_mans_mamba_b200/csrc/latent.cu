@@ -46,7 +46,8 @@ __global__ void __launch_bounds__(256)
                              const float* __restrict__ inv_freq, const int* __restrict__ positions,
                              const int* __restrict__ seq_of, const int* __restrict__ block_table, int max_blocks,
                              S* __restrict__ pool, int page_size, S* __restrict__ cq, int q_rank, int kv_rank,
-                             int rot_dim, int rot_dims, int Dp, int half) {
+                             int rot_dim, int rot_dims, int Dp, int half, const S* __restrict__ q, long long ld_q,
+                             S* __restrict__ q_out, int H, int dim) {
   __shared__ float red[32];
   __shared__ float sn_t[kLatentMaxPairs], cs_t[kLatentMaxPairs];
   pdl_launch_dependents();
@@ -87,6 +88,30 @@ __global__ void __launch_bounds__(256)
     }
     stf(k_row + i, kval);
     stf(v_row + i, vval);
+  }
+  // q != nullptr (queries that need no latent, q [T, H * (dim + rot_dim)]): latent_query_rot's work in the same
+  // launch, the rotated part of every head turned into q_out[t, h, kv_rank .. kv_rank + rot_dim), zeros up to Dp
+  if (q != nullptr) {
+    const int tail = Dp - kv_rank;
+    const S* qr = q + static_cast<long long>(t) * ld_q;
+    for (int e = threadIdx.x; e < H * tail; e += blockDim.x) {
+      const int h = e / tail, j = e - h * tail;
+      float val = 0.f;
+      if (j < rot_dim) {
+        const S* part = qr + static_cast<size_t>(h) * (dim + rot_dim) + dim;
+        const float a = ldf(part + j);
+        val = a;
+        if (j < rot_dims) {
+          int partner, pair;
+          bool second;
+          rot_partner(j, rot_dims, half, &partner, &pair, &second);
+          const float b = ldf(part + partner);
+          const float sn = sn_t[pair], cs = cs_t[pair];
+          val = second ? a * cs + b * sn : a * cs - b * sn;
+        }
+      }
+      stf(q_out + (static_cast<size_t>(t) * H + h) * Dp + kv_rank + j, val);
+    }
   }
 }
 
@@ -149,16 +174,19 @@ PMM_EXPORT int pmm_latent_norm_store(const void* x, long long ld_x, const void* 
                                      const float* kv_w, float eps, const float* inv_freq, const int* positions,
                                      const int* seq_of, const int* block_table, int max_blocks, void* pool,
                                      int page_size, void* cq, int T, int q_rank, int kv_rank, int rot_dim, int rot_dims,
-                                     int Dp, int half, int dtype, cudaStream_t stream) {
+                                     int Dp, int half, const void* q, long long ld_q, void* q_out, int H, int dim,
+                                     int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (q_rank < 0 || (q_rank > 0 && (!x || !q_w || !cq)) || kv_rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || rot_dims % 2 ||
       rot_dims > 2 * pmm::kLatentMaxPairs || (rot_dims > 0 && !inv_freq) || Dp < kv_rank + rot_dim || page_size <= 0)
     return PMM_ERR_BAD_ARGUMENT;
+  if (q && (!q_out || H <= 0 || dim <= 0)) return PMM_ERR_BAD_ARGUMENT;
   PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::latent_norm_store_kernel<S>, dim3(T), dim3(256), 0, stream,
                                                static_cast<const S*>(x), ld_x, static_cast<const S*>(kv), ld_kv, q_w,
                                                kv_w, eps, inv_freq, positions, seq_of, block_table, max_blocks,
                                                static_cast<S*>(pool), page_size, static_cast<S*>(cq), q_rank, kv_rank,
-                                               rot_dim, rot_dims, Dp, half));
+                                               rot_dim, rot_dims, Dp, half, static_cast<const S*>(q), ld_q,
+                                               static_cast<S*>(q_out), H, dim));
   return pmm::launch_status();
 }
 

@@ -137,7 +137,7 @@ _SIGNATURES = {
                         c_float, c_float, c_float, c_void_p, c_void_p, c_void_p],
     "pmm_latent_norm_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_int, c_int, c_void_p],
+                              c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_latent_query_rot": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_void_p],
     "pmm_head_gate": [c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
@@ -1598,12 +1598,13 @@ def latent_padded_dim(kv_rank: int, rot_dim: int) -> int:
 
 def latent_norm_store(q_lat: Tensor, kv_lat: Tensor, q_w: Tensor, kv_w: Tensor, eps: float, inv_freq: Optional[Tensor],
                       positions: Tensor, seq_of: Tensor, block_table: Tensor, pool: Tensor, cq: Tensor, kv_rank: int,
-                      rot_dim: int, rot_dims: int, half_layout: bool = False) -> None:
+                      rot_dim: int, rot_dims: int, half_layout: bool = False, queries: Optional[Tuple] = None) -> None:
     """cq = rms(q_lat) * q_w; the cache rows of the step's tokens: key row [rms(kv_lat[:kv_rank]) * kv_w | the last
     rot_dim entries of kv_lat, of which the first rot_dims turn in neighbouring pairs | 0], value row [the normed
     latent | 0], into ``pool`` [pages, 2, page_size, Dp].  Norms, angles, sines and cosines are float.
     ``half_layout``: entries (i, i + rot_dims/2) turn together instead of neighbours.  ``q_lat`` None (with q_w and
-    cq None): the queries have no latent, only the cache rows are made."""
+    cq None): the queries have no latent, only the cache rows are made.  ``queries`` = (q [T, heads * (dim +
+    rot_dim)], q_out [T, heads * Dp], heads, dim): `latent_query_rot`'s work for these queries in the same launch."""
     _cuda(q_lat, kv_lat, q_w, kv_w, inv_freq, positions, seq_of, block_table, pool, cq)
     T = kv_lat.shape[0]
     if q_lat is None:
@@ -1631,7 +1632,19 @@ def latent_norm_store(q_lat: Tensor, kv_lat: Tensor, q_w: Tensor, kv_w: Tensor, 
     _call("pmm_latent_norm_store", _ptr(q_lat), q_lat.stride(0) if q_lat is not None else 0, kv_lat.data_ptr(),
           kv_lat.stride(0), _ptr(q_w), kv_w.data_ptr(), float(eps), _ptr(inv_freq), positions.data_ptr(), seq_of.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], pool.data_ptr(), pool.shape[2], _ptr(cq), T, q_rank, int(kv_rank),
-          int(rot_dim), int(rot_dims), pool.shape[3], int(bool(half_layout)), _dt(kv_lat), _stream())
+          int(rot_dim), int(rot_dims), pool.shape[3], int(bool(half_layout)), *_latent_queries(queries, T, rot_dim, pool),
+          _dt(kv_lat), _stream())
+
+
+def _latent_queries(queries: Optional[Tuple], T: int, rot_dim: int, pool: Tensor):
+    if queries is None:
+        return None, 0, None, 0, 0
+    q, q_out, heads, dim = queries
+    _cuda(q, q_out)
+    if not (q.shape == (T, heads * (dim + rot_dim)) and q.stride(1) == 1 and q.dtype == q_out.dtype == pool.dtype
+            and q_out.shape == (T, heads * pool.shape[3]) and q_out.is_contiguous()):
+        raise KernelError("latent_norm_store: queries [T, H * (dim + rot_dim)], q_out contiguous [T, H * Dp] of the pool's type")
+    return q.data_ptr(), q.stride(0), q_out.data_ptr(), int(heads), int(dim)
 
 
 def latent_query_rot(q: Tensor, inv_freq: Optional[Tensor], positions: Tensor, q_out: Tensor, heads: int, dim: int,

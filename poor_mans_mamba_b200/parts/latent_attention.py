@@ -143,20 +143,25 @@ class LatentAttention(PagedSoftmaxAttention):
         c_kv = self.q_rank if self.q_rank > 0 else H * self.q_head     # the first column behind the queries' part
         c_g = c_kv + (0 if self.shared_kv else self.kv_lat)
         cq = ws.alloc((T, self.q_rank), proj.dtype) if self.q_rank > 0 else None
+        q_lat = ws.alloc((T, H * Dp), proj.dtype)
+        turned = False
         if not self.shared_kv:
             # (a layer that reads another's cache rows makes none: they hold the owner's latent and rotated key part)
+            # queries that need no latent are there already: their turned parts are made by the same launch
+            turned = self.q_rank == 0
             K.latent_norm_store(proj[:, :c_kv] if self.q_rank > 0 else None, proj[:, c_kv:c_g], self.q_norm_w,
                                 self.kv_norm_w, self.norm_eps, self.inv_freq, ctx.positions, ctx.seq_of, kv.block_table,
-                                kv.pool, cq, R, self.rot_dim, self.rot_dims, half_layout=self.half_layout)
+                                kv.pool, cq, R, self.rot_dim, self.rot_dims, half_layout=self.half_layout,
+                                queries=(proj[:, :c_kv], q_lat, H, self.dim) if turned else None)
         if self.q_rank > 0:
             q = ws.alloc((T, H * self.q_head), proj.dtype)
             streaming.linear(cq, self.w_uq, q, ctx)
         else:
             q = proj[:, :c_kv]
-        q_lat = ws.alloc((T, H * Dp), proj.dtype)
         K.head_linear(q.unflatten(1, (H, self.q_head))[:, :, :self.dim], self.w_uk, q_lat.view(T, H, Dp)[:, :, :R])
-        K.latent_query_rot(q, self.inv_freq, ctx.positions, q_lat, H, self.dim, self.rot_dim, self.rot_dims, R, Dp,
-                           half_layout=self.half_layout)
+        if not turned:
+            K.latent_query_rot(q, self.inv_freq, ctx.positions, q_lat, H, self.dim, self.rot_dim, self.rot_dims, R, Dp,
+                               half_layout=self.half_layout)
         attn = ws.alloc((T, H * Dp), proj.dtype)
         self._attend(q_lat, kv, ctx, attn)
         heads = ws.alloc((T, self.o_dim), proj.dtype)

@@ -219,6 +219,13 @@ def test_latent_rows_with_halves_turned_and_queries_without_a_latent(dtype, kv_r
     K.latent_query_rot(q, inv, i32(positions), out, H, dim, rot_dim, rot_dims, kv_rank, Dp, half_layout=True)
     want = P.rotate_halves(q.double().cpu().view(T, H, dim + rot_dim)[:, :, dim:], torch.tensor(positions), rot_dims, base)
     close(out.view(T, H, Dp)[:, :, kv_rank:kv_rank + rot_dim], want, dtype, "turned query part", f32=3e-5)
+    # both in one launch: the rows and the queries' turned parts
+    pool2 = torch.full_like(pool, 7.0)
+    out2 = torch.full((T, H * Dp), 3.0, dtype=dtype, device=DEV)
+    K.latent_norm_store(None, kvl, None, kw.to(DEV), eps, inv, i32(positions), i32(seq), table, pool2, None, kv_rank, rot_dim,
+                        rot_dims, half_layout=True, queries=(q, out2, H, dim))
+    used = sorted({int(table[seq[t], positions[t] // page]) for t in range(T)})
+    assert torch.equal(pool2[used], pool[used]) and torch.equal(out2, out)
 
 
 # ----------------------------------------------------------------------------- window with kept first tokens
