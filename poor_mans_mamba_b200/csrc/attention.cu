@@ -179,6 +179,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   float* qw = qs + warp * Dh;
   const size_t q_off = (static_cast<size_t>(t) * Hq + hq) * Dh;
   for (int d = lane; d < Dh; d += 32) qw[d] = ldf(q + q_off + d);
+  // the windowed result and its maximum and sum are asked for now: their latency hides behind the walk over the keys
+  const float m_w = lse[(static_cast<size_t>(t) * Hq + hq) * 2], l_w = lse[(static_cast<size_t>(t) * Hq + hq) * 2 + 1];
+  float prev[kAttnMaxAcc];
+#pragma unroll
+  for (int i = 0; i < kAttnMaxAcc; ++i) {
+    const int d = lane + 32 * i;
+    prev[i] = d < Dh ? ldf(out + q_off + d) : 0.f;
+  }
   __syncwarp();
   float m = -CUDART_INF_F, l = 0.f;
   float acc[kAttnMaxAcc];
@@ -212,7 +220,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
     }
     m = m_new;
   }
-  const float m_w = lse[(static_cast<size_t>(t) * Hq + hq) * 2], l_w = lse[(static_cast<size_t>(t) * Hq + hq) * 2 + 1];
   const float big = fmaxf(m, l_w > 0.f ? m_w : -CUDART_INF_F);
   const float a = l_w > 0.f ? l_w * expf(m_w - big) : 0.f;  // weight of the windowed result
   const float b = expf(m - big);
@@ -220,7 +227,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
 #pragma unroll
   for (int i = 0; i < kAttnMaxAcc; ++i) {
     const int d = lane + 32 * i;
-    if (d < Dh) stf(out + q_off + d, (ldf(out + q_off + d) * a + acc[i] * b) * inv);
+    if (d < Dh) stf(out + q_off + d, (prev[i] * a + acc[i] * b) * inv);
   }
 }
 
