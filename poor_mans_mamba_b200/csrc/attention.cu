@@ -244,7 +244,10 @@ PMM_EXPORT int pmm_kept_first_merge(const void* q, const void* pool, const int* 
   if (head_blocks > 65535) return PMM_ERR_BAD_ARGUMENT;
   const size_t smem = static_cast<size_t>(pmm::kAttnWarps) * Dh * sizeof(float);
   PMM_DISPATCH_DTYPE(dtype, S, {
-    auto kern = Dh <= 256 ? pmm::kept_first_merge_kernel<S, 8> : pmm::kept_first_merge_kernel<S, 16>;
+    // (sums a lane: two for head sizes up to 64, four up to 128: the walk is short and issue-bound otherwise)
+    auto kern = Dh <= 64 ? pmm::kept_first_merge_kernel<S, 2>
+              : Dh <= 128 ? pmm::kept_first_merge_kernel<S, 4>
+              : Dh <= 256 ? pmm::kept_first_merge_kernel<S, 8> : pmm::kept_first_merge_kernel<S, 16>;
     pmm::launch_pdl(kern, dim3(T, head_blocks), dim3(pmm::kAttnWarps * 32), smem, stream, static_cast<const S*>(q),
                     static_cast<const S*>(pool), block_table, max_blocks, positions, seq_of, static_cast<S*>(out), lse,
                     scale, window, keep_first, page_size, Hq, Hkv, Dh);

@@ -167,8 +167,10 @@ __global__ void add_postnorm_rmsnorm_kernel(float* __restrict__ h, const S* __re
   for (int i = threadIdx.x; i < D; i += blockDim.x) stf(o + i, buf[i] * inv * w[i]);
 }
 
-// The same for widths that are a multiple of 4: four elements per thread and access.
-template <typename S>
+// The same for widths that are a multiple of 4: four elements per thread and access.  A thread's first P pieces
+// (the launcher takes the smallest P of 1, 2, 4 that covers the row) stay in registers from the first read to the
+// last write; with P = 4 pieces beyond wait in shared memory.
+template <typename S, int P>
 __global__ void add_postnorm_rmsnorm_vec_kernel(float* __restrict__ h, const S* __restrict__ a, float sa,
                                                 const S* __restrict__ b, float sb, const float* __restrict__ post_w,
                                                 float post_eps, const float* __restrict__ w, float eps,
@@ -179,56 +181,71 @@ __global__ void add_postnorm_rmsnorm_vec_kernel(float* __restrict__ h, const S* 
   pdl_wait();
   const int r = blockIdx.x;
   const size_t src = static_cast<size_t>(rows ? rows[r] : r) * D;
-  float ss = 0.f;
-  for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) {
+  const int step = blockDim.x * 4;
+  auto branches = [&](int i) {
     float4 s = ld4(a + src + i);
     s.x *= sa; s.y *= sa; s.z *= sa; s.w *= sa;
     if (b) {
       const float4 x = ld4(b + src + i);
       s.x += sb * x.x; s.y += sb * x.y; s.z += sb * x.z; s.w += sb * x.w;
     }
-    *reinterpret_cast<float4*>(buf + i) = s;
-    ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
-  }
-  // (the stream's row is asked for before the reduction, so that its latency hides behind it: the first four
-  // pieces of a thread, which is all of them up to a width of 16 pieces a thread)
-  float4 hv[4];
+    return s;
+  };
+  auto sq = [](float4 v) { return v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; };
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 v[P], hv[P];
+  float ss = 0.f;
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const int i = (threadIdx.x + c * blockDim.x) * 4;
-    hv[c] = (h && i < D) ? ld4(h + src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c = 0; c < P; ++c) {
+    const int i = threadIdx.x * 4 + c * step;
+    v[c] = i < D ? branches(i) : zero;
+    // (the stream's row is asked for before the reduction, so that its latency hides behind it)
+    hv[c] = (h && i < D) ? ld4(h + src + i) : zero;
+    ss += sq(v[c]);
+  }
+  if (P == 4) {
+    for (int i = threadIdx.x * 4 + 4 * step; i < D; i += step) {
+      const float4 s = branches(i);
+      *reinterpret_cast<float4*>(buf + i) = s;
+      ss += sq(s);
+    }
   }
   const float inv_p = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(D) + post_eps);
   float sv = 0.f;
-  auto join = [&](int i, float4 x) {
-    const float4 s = *reinterpret_cast<const float4*>(buf + i);
+  auto join = [&](int i, float4 s, float4 x) {
     const float4 g = ld4(post_w + i);
-    float4 v = make_float4(s.x * inv_p * g.x, s.y * inv_p * g.y, s.z * inv_p * g.z, s.w * inv_p * g.w);
-    if (h) {
-      v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
-      if (!rows) st4(h + src + i, v);
-    }
-    *reinterpret_cast<float4*>(buf + i) = v;
-    sv += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    float4 y = make_float4(s.x * inv_p * g.x + x.x, s.y * inv_p * g.y + x.y, s.z * inv_p * g.z + x.z, s.w * inv_p * g.w + x.w);
+    if (h && !rows) st4(h + src + i, y);
+    sv += sq(y);
+    return y;
   };
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const int i = (threadIdx.x + c * blockDim.x) * 4;
-    if (i < D) join(i, hv[c]);
+  for (int c = 0; c < P; ++c) {
+    const int i = threadIdx.x * 4 + c * step;
+    if (i < D) v[c] = join(i, v[c], hv[c]);
   }
-  for (int i = (threadIdx.x + 4 * blockDim.x) * 4; i < D; i += blockDim.x * 4)
-    join(i, h ? ld4(h + src + i) : make_float4(0.f, 0.f, 0.f, 0.f));
+  if (P == 4) {
+    for (int i = threadIdx.x * 4 + 4 * step; i < D; i += step)
+      *reinterpret_cast<float4*>(buf + i) = join(i, *reinterpret_cast<const float4*>(buf + i), h ? ld4(h + src + i) : zero);
+  }
   if (!out) return;
   S* o = out + static_cast<size_t>(r) * D;
-  if (!w) {
-    for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) st4(o + i, *reinterpret_cast<const float4*>(buf + i));
-    return;
+  float inv = 1.f;
+  if (w) inv = 1.0f / sqrtf(block_sum(sv, red) / static_cast<float>(D) + eps);
+  auto write = [&](int i, float4 y) {
+    if (w) {
+      const float4 g = ld4(w + i);
+      y = make_float4(y.x * inv * g.x, y.y * inv * g.y, y.z * inv * g.z, y.w * inv * g.w);
+    }
+    st4(o + i, y);
+  };
+#pragma unroll
+  for (int c = 0; c < P; ++c) {
+    const int i = threadIdx.x * 4 + c * step;
+    if (i < D) write(i, v[c]);
   }
-  const float inv = 1.0f / sqrtf(block_sum(sv, red) / static_cast<float>(D) + eps);
-  for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) {
-    const float4 v = *reinterpret_cast<const float4*>(buf + i);
-    const float4 g = ld4(w + i);
-    st4(o + i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+  if (P == 4) {
+    for (int i = threadIdx.x * 4 + 4 * step; i < D; i += step) write(i, *reinterpret_cast<const float4*>(buf + i));
   }
 }
 
@@ -291,7 +308,10 @@ PMM_EXPORT int pmm_add_postnorm_rmsnorm(void* h, const void* a, float sa, const 
   auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool vec = D % 4 == 0 && aligned(h) && aligned(a) && aligned(b) && aligned(out) && aligned(w) && aligned(post_w);
   PMM_DISPATCH_DTYPE(dtype, S, {
-    auto kern = vec ? pmm::add_postnorm_rmsnorm_vec_kernel<S> : pmm::add_postnorm_rmsnorm_kernel<S>;
+    const int pieces = (D + threads * 4 - 1) / (threads * 4);
+    auto kern = !vec ? pmm::add_postnorm_rmsnorm_kernel<S>
+              : pieces <= 1 ? pmm::add_postnorm_rmsnorm_vec_kernel<S, 1>
+              : pieces <= 2 ? pmm::add_postnorm_rmsnorm_vec_kernel<S, 2> : pmm::add_postnorm_rmsnorm_vec_kernel<S, 4>;
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
       if (e != cudaSuccess) return static_cast<int>(e);

@@ -49,7 +49,7 @@ def test_embedding_with_its_norm(dtype, D):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("D,branches", [(44, 1), (72, 2), (328, 1), (1030, 2)])
+@pytest.mark.parametrize("D,branches", [(44, 1), (72, 2), (328, 1), (1030, 2), (2048, 1), (3072, 2), (5000, 2), (9000, 1)])
 def test_post_norm_of_a_sublayer_and_norm_of_the_stream_in_one_launch(dtype, D, branches):
     """x <- x + rms(sum of branches) * w_post, out = rms(x) * w: for all rows, for chosen rows (the stream is
     then left alone), without a following norm, and without a stream."""
